@@ -149,14 +149,21 @@ class GroupSpec:
     value_head_dim: Optional[int] = None    # elements of a cached value row (None: head_dim; 0: no values)
     dtype: object = None        # storage dtype of the pages (None: the engine's run dtype)
     tag: str = ""               # groups with different tags are never merged
+    tokens_per_row: int = 1     # > 1: one cached row per so many positions (a cache of summaries)
 
     def key(self):
-        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.value_head_dim, self.dtype, self.tag)
+        return (self.kind, self.num_kv_heads, self.head_dim, self.window, self.value_head_dim, self.dtype, self.tag,
+                self.tokens_per_row)
+
+    def page_rows(self, page_tokens: int) -> int:
+        """Rows a page holds: one per token, or one per ``tokens_per_row`` positions."""
+        return -(-page_tokens // max(int(self.tokens_per_row), 1))
 
     def page_elements(self, page_tokens: int):
         """Elements of one page of one layer: (key pool, value pool)."""
         vd = self.head_dim if self.value_head_dim is None else self.value_head_dim
-        return (self.num_kv_heads * page_tokens * self.head_dim, self.num_kv_heads * page_tokens * vd)
+        rows = self.page_rows(page_tokens)
+        return (self.num_kv_heads * rows * self.head_dim, self.num_kv_heads * rows * vd)
 
 
 @dataclass(frozen=True)

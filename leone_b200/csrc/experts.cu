@@ -23,9 +23,9 @@ __device__ __forceinline__ float silu_e(float z) { return z / (1.f + expf(-z)); 
 
 // One warp per token: scores from the router's fp32 logits, then the `top` largest.
 __global__ void __launch_bounds__(128)
-select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int experts, int top, int softmax,
-              int renormalize, int groups, int keep, float weight_scale, int* __restrict__ chosen,
-              float* __restrict__ weight) {
+select_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ bias, int n_tokens, int experts,
+              int top, int softmax, int renormalize, int groups, int keep, float weight_scale,
+              int* __restrict__ chosen, float* __restrict__ weight) {
   pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
   pdl_wait();
   extern __shared__ __align__(16) float smem[];
@@ -34,17 +34,19 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
   if (t >= n_tokens) return;
   float* sc = smem + (size_t)warp * experts;
   const float* row = logits + (size_t)t * ldl;
-  if (softmax) {
+  for (int e = lane; e < experts; e += 32) sc[e] = row[e] + (bias != nullptr ? bias[e] : 0.f);
+  __syncwarp();
+  if (softmax == 1) {
     float m = -INFINITY;
-    for (int e = lane; e < experts; e += 32) m = fmaxf(m, row[e]);
+    for (int e = lane; e < experts; e += 32) m = fmaxf(m, sc[e]);
     m = warp_max(m);
     float sum = 0.f;
-    for (int e = lane; e < experts; e += 32) sum += expf(row[e] - m);
+    for (int e = lane; e < experts; e += 32) sum += expf(sc[e] - m);
     sum = warp_sum(sum);
-    for (int e = lane; e < experts; e += 32) sc[e] = expf(row[e] - m) / sum;
-  } else {
-    for (int e = lane; e < experts; e += 32) sc[e] = 1.f / (1.f + expf(-row[e]));
-  }
+    for (int e = lane; e < experts; e += 32) sc[e] = expf(sc[e] - m) / sum;
+  } else if (softmax == 0) {
+    for (int e = lane; e < experts; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
+  }                              // softmax == 2: the logits themselves are compared
   __syncwarp();
   if (groups > 1 && keep < groups) {
     // what every group is worth, then the groups that are not kept lose their experts
@@ -64,7 +66,7 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
     }
     __syncwarp();
   }
-  float total = 0.f;
+  float total = 0.f, first = 0.f;
   for (int j = 0; j < top; ++j) {
     float best = -INFINITY;
     int at = 0x7fffffff;
@@ -78,6 +80,10 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
       const int oa = __shfl_xor_sync(0xffffffffu, at, o);
       if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
     }
+    if (softmax == 2) {          // the weights are the softmax over the chosen logits only
+      if (j == 0) first = best;  // the largest of them
+      best = expf(best - first);
+    }
     if (lane == 0) {
       chosen[(size_t)t * top + j] = at;
       weight[(size_t)t * top + j] = best;
@@ -86,7 +92,7 @@ select_kernel(const float* __restrict__ logits, int ldl, int n_tokens, int exper
     total += best;
     __syncwarp();
   }
-  if (renormalize)
+  if (renormalize || softmax == 2)
     for (int j = lane; j < top; j += 32) weight[(size_t)t * top + j] /= total;
   if (weight_scale != 1.f) {
     __syncwarp();
@@ -496,15 +502,17 @@ using namespace leone;
 
 // logits: fp32 [n_tokens, ldl] (the router's product); chosen, weight: [n_tokens * top].
 // groups <= 1 (or keep == groups): every expert can be chosen.
-extern "C" int leone_experts_select(const float* logits, int ldl, int n_tokens, int experts, int top, int softmax,
-                                    int renormalize, int groups, int keep, float weight_scale, int* chosen,
+// softmax: 0 sigmoid scores, 1 softmax over all experts, 2 the logits are ranked and the weights are the
+// softmax over the chosen ones.  bias: fp32 [experts] added to the logits first, or null.
+extern "C" int leone_experts_select(const float* logits, int ldl, const float* bias, int n_tokens, int experts, int top,
+                                    int softmax, int renormalize, int groups, int keep, float weight_scale, int* chosen,
                                     float* weight, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (experts <= 0 || top <= 0 || top > experts || experts > 2048 || ldl < experts) return kRefusedSize;
   if (groups < 1) groups = 1;
   if (experts % groups != 0 || keep < 1 || keep > groups || top > experts / groups * keep) return kRefusedSize;
   launch_kernel(select_kernel, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * (size_t)(experts + groups), stream,
-      logits, ldl, n_tokens, experts, top, softmax, renormalize, groups, keep, weight_scale, chosen, weight);
+      logits, ldl, bias, n_tokens, experts, top, softmax, renormalize, groups, keep, weight_scale, chosen, weight);
   return launch_result();
 }
 

@@ -1,0 +1,299 @@
+// A short causal convolution over time on every channel, with the last taps - 1 inputs of every
+// sequence kept as fixed-size state between steps; and the minGRU recurrence.
+//
+//   leone_short_conv:        y_t[c] = (add_input ? x_t[c] : 0) + sum_j w[c, j] x_(t - taps + 1 + j)[c],
+//                            inputs before a sequence's start are zero; an input before the step's
+//                            first token comes from the state
+//   leone_short_conv_state:  the state after the step: the last taps - 1 inputs of every sequence
+//                            (older rows move up when the step brought fewer than taps - 1 tokens)
+//   leone_min_gru:           z = sigmoid(pz + bz), u = px + bx, c = u >= 0 ? u + 1/2 : sigmoid(u),
+//                            S_t = (1 - z) S_(t-1) + z c element by element, state fp32 per slot,
+//                            out_t = out_scale * S_t * silu(pg)
+//   leone_scale_rows:        a[t, :] *= scale * sigmoid(gate[t])  (gate: one fp32 logit per row)
+//   leone_add_scaled:        x += scale * y  (fp32)
+//
+// The state is [slots, taps - 1, channels] fp32, row taps - 2 the newest input.  Weights are fp32
+// [channels, taps].  All sums are fp32 in ascending j, so a token's result does not depend on how
+// its sequence was cut into steps.  The convolution does not write the state (tokens at a step's
+// start still read it); the state kernel runs after it.
+#include "common.cuh"
+
+namespace leone {
+
+constexpr int kConvThreads = 128;
+constexpr int kMaxTaps = 16;
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(kConvThreads)
+short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ state,
+                  TO* __restrict__ out, int ldo, const int* __restrict__ q_start, const int* __restrict__ seq_of_token,
+                  const int* __restrict__ slot_ids, int channels, int taps, int add_input, int n_seqs, int n_slots,
+                  int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, c = blockIdx.y * kConvThreads + threadIdx.x;
+  if (c >= channels) return;
+  const int s = seq_of_token[t];
+  if (s < 0 || s >= n_seqs) {
+    if (threadIdx.x == 0) set_status(status, kBadSequence, t, s);
+    return;
+  }
+  const int slot = slot_ids[s];
+  if (slot < 0 || slot >= n_slots) {
+    if (threadIdx.x == 0) set_status(status, kBadSequence, t, slot);
+    return;
+  }
+  const int local = t - q_start[s];                 // tokens of the sequence in this step before this one
+  const float* st = state + (size_t)slot * (taps - 1) * channels;
+  float acc = 0.f;
+  for (int j = 0; j < taps; ++j) {
+    const int back = taps - 1 - j;
+    float v;
+    if (back <= local) v = to_float<TI>(x[(size_t)(t - back) * ldx + c]);
+    else v = st[(size_t)(taps - 1 + local - back) * channels + c];
+    acc = fmaf(w[(size_t)c * taps + j], v, acc);
+  }
+  if (add_input) acc += to_float<TI>(x[(size_t)t * ldx + c]);
+  out[(size_t)t * ldo + c] = from_float<TO>(acc);
+}
+
+template <typename TI>
+__global__ void __launch_bounds__(kConvThreads)
+short_conv_state_kernel(const TI* __restrict__ x, int ldx, float* __restrict__ state, const int* __restrict__ q_start,
+                        const int* __restrict__ slot_ids, int channels, int taps, int n_slots, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.x, c = blockIdx.y * kConvThreads + threadIdx.x;
+  if (c >= channels) return;
+  const int slot = slot_ids[s];
+  if (slot < 0 || slot >= n_slots) {
+    if (threadIdx.x == 0) set_status(status, kBadSequence, s, slot);
+    return;
+  }
+  const int first = q_start[s], len = q_start[s + 1] - first, keep = taps - 1;
+  float* st = state + (size_t)slot * keep * channels;
+  float rows[kMaxTaps];
+#pragma unroll
+  for (int r = 0; r < kMaxTaps; ++r) {
+    if (r < keep) {
+      const int local = len - keep + r;             // which of the step's tokens lands in row r
+      rows[r] = local >= 0 ? to_float<TI>(x[(size_t)(first + local) * ldx + c]) : st[(size_t)(r + len) * channels + c];
+    }
+  }
+#pragma unroll
+  for (int r = 0; r < kMaxTaps; ++r)
+    if (r < keep) st[(size_t)r * channels + c] = rows[r];
+}
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(kConvThreads)
+min_gru_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g_off, const float* __restrict__ z_b,
+               const float* __restrict__ x_b, float* __restrict__ state, TO* __restrict__ out, int ldo,
+               const int* __restrict__ q_start, const int* __restrict__ slot_ids, int width, int n_slots,
+               float out_scale, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
+  if (c >= width) return;
+  const int slot = slot_ids[s];
+  if (slot < 0 || slot >= n_slots) {
+    if (threadIdx.x == 0) set_status(status, kBadSequence, s, slot);
+    return;
+  }
+  const int first = q_start[s], last = q_start[s + 1];
+  const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
+  float S = state[(size_t)slot * width + c];
+  for (int t = first; t < last; ++t) {
+    const TP* row = proj + (size_t)t * ldp;
+    const float z = sigmoid_f(to_float<TP>(row[z_off + c]) + bz);
+    const float u = to_float<TP>(row[x_off + c]) + bx;
+    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+    S = (1.f - z) * S + z * cand;
+    const float g = to_float<TP>(row[g_off + c]);
+    out[(size_t)t * ldo + c] = from_float<TO>(out_scale * S * (g * sigmoid_f(g)));
+  }
+  state[(size_t)slot * width + c] = S;
+}
+
+// The recurrence cut into chunks that run side by side.  S_t = a_t S_(t-1) + b_t with a = 1 - z, b = z c:
+// pass 1 gives every chunk its (product of a, S at its end from a zero start); pass 2 walks a sequence's
+// chunks in order and leaves the state at each chunk's start; pass 3 walks every chunk from there and
+// writes the outputs.  The per-token arithmetic of pass 3 is that of the unchunked kernel.
+template <typename TP>
+__global__ void __launch_bounds__(kConvThreads)
+min_gru_chunk_sums_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, const float* __restrict__ z_b,
+                          const float* __restrict__ x_b, const int* __restrict__ chunk_first,
+                          const int* __restrict__ chunk_last, float* __restrict__ chunk_a, float* __restrict__ chunk_s,
+                          int width) {
+  pdl_trigger();
+  pdl_wait();
+  const int k = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
+  if (c >= width) return;
+  const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
+  float A = 1.f, S = 0.f;
+  for (int t = chunk_first[k]; t < chunk_last[k]; ++t) {
+    const TP* row = proj + (size_t)t * ldp;
+    const float z = sigmoid_f(to_float<TP>(row[z_off + c]) + bz);
+    const float u = to_float<TP>(row[x_off + c]) + bx;
+    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+    S = (1.f - z) * S + z * cand;
+    A *= 1.f - z;
+  }
+  chunk_a[(size_t)k * width + c] = A;
+  chunk_s[(size_t)k * width + c] = S;
+}
+
+__global__ void __launch_bounds__(kConvThreads)
+min_gru_chunk_prefix_kernel(const int* __restrict__ seq_chunk_start, const int* __restrict__ slot_ids,
+                            const float* __restrict__ chunk_a, float* __restrict__ chunk_s, float* __restrict__ state,
+                            int width, int n_slots, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int s = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
+  if (c >= width) return;
+  const int slot = slot_ids[s];
+  if (slot < 0 || slot >= n_slots) {
+    if (threadIdx.x == 0) set_status(status, kBadSequence, s, slot);
+    return;
+  }
+  float S = state[(size_t)slot * width + c];
+  for (int k = seq_chunk_start[s]; k < seq_chunk_start[s + 1]; ++k) {
+    const float end = chunk_a[(size_t)k * width + c] * S + chunk_s[(size_t)k * width + c];
+    chunk_s[(size_t)k * width + c] = S;            // from here on: the state at the chunk's start
+    S = end;
+  }
+  state[(size_t)slot * width + c] = S;
+}
+
+template <typename TP, typename TO>
+__global__ void __launch_bounds__(kConvThreads)
+min_gru_chunk_out_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g_off,
+                         const float* __restrict__ z_b, const float* __restrict__ x_b, const int* __restrict__ chunk_first,
+                         const int* __restrict__ chunk_last, const float* __restrict__ chunk_s, TO* __restrict__ out,
+                         int ldo, int width, float out_scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int k = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
+  if (c >= width) return;
+  const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
+  float S = chunk_s[(size_t)k * width + c];
+  for (int t = chunk_first[k]; t < chunk_last[k]; ++t) {
+    const TP* row = proj + (size_t)t * ldp;
+    const float z = sigmoid_f(to_float<TP>(row[z_off + c]) + bz);
+    const float u = to_float<TP>(row[x_off + c]) + bx;
+    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+    S = (1.f - z) * S + z * cand;
+    const float g = to_float<TP>(row[g_off + c]);
+    out[(size_t)t * ldo + c] = from_float<TO>(out_scale * S * (g * sigmoid_f(g)));
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+scale_rows_kernel(T* __restrict__ a, int lda, int cols, const float* __restrict__ gate, int ldg, float scale) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float f = gate != nullptr ? scale * sigmoid_f(gate[(size_t)t * ldg]) : scale;
+  for (int c = threadIdx.x; c < cols; c += blockDim.x)
+    a[(size_t)t * lda + c] = from_float<T>(to_float<T>(a[(size_t)t * lda + c]) * f);
+}
+
+__global__ void __launch_bounds__(256)
+add_scaled_kernel(float* __restrict__ x, const float* __restrict__ y, long long n, float scale) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] = fmaf(scale, y[i], x[i]);
+}
+
+}  // namespace leone
+
+using namespace leone;
+
+extern "C" int leone_add_scaled(float* x, const float* y, long long n, float scale, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  const long long blocks = (n + 255) / 256;
+  return launch_kernel(add_scaled_kernel, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream, x, y,
+                       n, scale);
+}
+
+// in_dtype / out_dtype: 0 float32, 1 bfloat16.
+extern "C" int leone_short_conv(int in_dtype, int out_dtype, const void* x, int ldx, const float* w, const float* state,
+                                void* out, int ldo, const int* q_start, const int* seq_of_token, const int* slot_ids,
+                                int n_tokens, int channels, int taps, int add_input, int n_seqs, int n_slots,
+                                int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (channels <= 0 || taps < 1 || taps > kMaxTaps || ldx < channels || ldo < channels) return kRefusedSize;
+  if (taps > 1 && state == nullptr) return kRefusedSize;
+  const dim3 grid(n_tokens, (channels + kConvThreads - 1) / kConvThreads);
+#define LAUNCH(TI, TO)                                                                                            \
+  return launch_kernel(short_conv_kernel<TI, TO>, grid, dim3(kConvThreads), 0, stream, (const TI*)x, ldx, w, state, \
+                       (TO*)out, ldo, q_start, seq_of_token, slot_ids, channels, taps, add_input, n_seqs, n_slots, status)
+  if (in_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
+  if (in_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  if (in_dtype == 1 && out_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+  if (in_dtype == 1 && out_dtype == 0) LAUNCH(__nv_bfloat16, float);
+#undef LAUNCH
+  return kRefusedDtype;
+}
+
+extern "C" int leone_short_conv_state(int in_dtype, const void* x, int ldx, float* state, const int* q_start,
+                                      const int* slot_ids, int n_seqs, int channels, int taps, int n_slots, int* status,
+                                      cudaStream_t stream) {
+  if (n_seqs <= 0 || taps <= 1) return 0;
+  if (channels <= 0 || taps > kMaxTaps || ldx < channels) return kRefusedSize;
+  const dim3 grid(n_seqs, (channels + kConvThreads - 1) / kConvThreads);
+  if (in_dtype == 0)
+    return launch_kernel(short_conv_state_kernel<float>, grid, dim3(kConvThreads), 0, stream, (const float*)x, ldx, state,
+                         q_start, slot_ids, channels, taps, n_slots, status);
+  if (in_dtype == 1)
+    return launch_kernel(short_conv_state_kernel<__nv_bfloat16>, grid, dim3(kConvThreads), 0, stream,
+                         (const __nv_bfloat16*)x, ldx, state, q_start, slot_ids, channels, taps, n_slots, status);
+  return kRefusedDtype;
+}
+
+// n_chunks == 0: one thread walks all of a sequence's tokens.  Otherwise chunk_first / chunk_last (token rows)
+// [n_chunks] and seq_chunk_start [n_seqs + 1] describe the cut, and chunk_a / chunk_s are fp32 [n_chunks, width].
+extern "C" int leone_min_gru(int proj_dtype, int out_dtype, const void* proj, int ldp, int z_off, int x_off, int g_off,
+                             const float* z_b, const float* x_b, float* state, void* out, int ldo, const int* q_start,
+                             const int* slot_ids, int n_seqs, int width, int n_slots, float out_scale, int n_chunks,
+                             const int* chunk_first, const int* chunk_last, const int* seq_chunk_start, float* chunk_a,
+                             float* chunk_s, int* status, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  if (width <= 0 || ldp < width || ldo < width || n_seqs > 65535 || n_chunks > 65535) return kRefusedSize;
+  const unsigned cols = (width + kConvThreads - 1) / kConvThreads;
+#define LAUNCH(TP, TO)                                                                                                  \
+  {                                                                                                                     \
+    if (n_chunks == 0)                                                                                                  \
+      return launch_kernel(min_gru_kernel<TP, TO>, dim3(cols, n_seqs), dim3(kConvThreads), 0, stream, (const TP*)proj,  \
+                           ldp, z_off, x_off, g_off, z_b, x_b, state, (TO*)out, ldo, q_start, slot_ids, width, n_slots, \
+                           out_scale, status);                                                                          \
+    launch_kernel(min_gru_chunk_sums_kernel<TP>, dim3(cols, n_chunks), dim3(kConvThreads), 0, stream, (const TP*)proj,  \
+                  ldp, z_off, x_off, z_b, x_b, chunk_first, chunk_last, chunk_a, chunk_s, width);                       \
+    launch_kernel(min_gru_chunk_prefix_kernel, dim3(cols, n_seqs), dim3(kConvThreads), 0, stream, seq_chunk_start,      \
+                  slot_ids, (const float*)chunk_a, chunk_s, state, width, n_slots, status);                             \
+    return launch_kernel(min_gru_chunk_out_kernel<TP, TO>, dim3(cols, n_chunks), dim3(kConvThreads), 0, stream,         \
+                         (const TP*)proj, ldp, z_off, x_off, g_off, z_b, x_b, chunk_first, chunk_last,                  \
+                         (const float*)chunk_s, (TO*)out, ldo, width, out_scale);                                       \
+  }
+  if (proj_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
+  if (proj_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
+  if (proj_dtype == 1 && out_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);
+#undef LAUNCH
+  return kRefusedDtype;
+}
+
+extern "C" int leone_scale_rows(int dtype, void* a, int lda, int n_rows, int cols, const float* gate, int ldg,
+                                float scale, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (cols <= 0 || lda < cols) return kRefusedSize;
+  if (dtype == 0)
+    return launch_kernel(scale_rows_kernel<float>, dim3(n_rows), dim3(256), 0, stream, (float*)a, lda, cols, gate, ldg, scale);
+  if (dtype == 1)
+    return launch_kernel(scale_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(256), 0, stream, (__nv_bfloat16*)a, lda,
+                         cols, gate, ldg, scale);
+  return kRefusedDtype;
+}

@@ -22,7 +22,7 @@ import torch
 
 from ..cache.pages import CacheManager, GroupSpec, OutOfPages
 from ..cache.slots import SlotRecords
-from ..parts.base import FixedState, PagedCacheView, PagedKV, Runtime, StateView
+from ..parts.base import BundleView, CacheBundle, FixedState, PagedCacheView, PagedKV, Runtime, StateView
 from ..parts.spec import ModelSpec
 from ..registry import config_from_folder, spec_from_config
 from ..weights.loader import check_names_and_shapes, load_checkpoint, target_dtype
@@ -82,30 +82,42 @@ class Engine:
         self.max_requests = max_requests
         plan = self.model.cache_plan()
         group_specs: List[GroupSpec] = []
-        self._run_group: Dict[int, tuple] = {}      # run position -> (gid, index within group)
-        self._run_state: Dict[int, torch.Tensor] = {}
+        # run position -> what its cache is bound to: ("paged", gid, index within the group, tokens per row),
+        # ("state", key into _run_state), ("bundle", {name: binding}) or None
+        self._run_binding: Dict[int, object] = {}
+        self._run_state: Dict[object, torch.Tensor] = {}
         self._run_source: Dict[int, int] = {}       # run position -> position whose cache it reads
-        state_shapes: Dict[int, tuple] = {}
-        for pos, (req, source) in enumerate(plan):
-            if source is not None:
-                self._run_source[pos] = source
-            elif isinstance(req, PagedKV):
+        state_shapes: Dict[object, tuple] = {}
+
+        def bind(key, req):
+            if req is None:
+                return None
+            if isinstance(req, CacheBundle):
+                return ("bundle", {name: bind((*key, name), member) for name, member in req.members.items()})
+            if isinstance(req, PagedKV):
                 # the part says what it caches (widths, dtype, when pages go back); equal requests share a group
                 r = req.resolved(self.dtype)
                 gs = GroupSpec(r.lifetime, r.num_kv_heads, r.head_dim, r.window, value_head_dim=r.value_head_dim,
-                               dtype=r.dtype, tag=r.tag)
+                               dtype=r.dtype, tag=r.tag, tokens_per_row=r.tokens_per_row)
                 for gid, existing in enumerate(group_specs):
                     if existing.key() == gs.key():
                         break
                 else:
                     gid = len(group_specs)
                     group_specs.append(gs)
-                self._run_group[pos] = (gid, len(group_specs[gid].layers))
-                group_specs[gid].layers.append(pos)
-            elif isinstance(req, FixedState):
-                state_shapes[pos] = (max_requests,) + tuple(int(d) for d in req.shape)
-            elif req is not None:
-                raise TypeError(f"run position {pos}: unknown cache request {req!r}")
+                group_specs[gid].layers.append(key[0])
+                return ("paged", gid, len(group_specs[gid].layers) - 1, r.tokens_per_row)
+            if isinstance(req, FixedState):
+                skey = key[0] if len(key) == 1 else key
+                state_shapes[skey] = (max_requests,) + tuple(int(d) for d in req.shape)
+                return ("state", skey)
+            raise TypeError(f"run position {key[0]}: unknown cache request {req!r}")
+
+        for pos, (req, source) in enumerate(plan):
+            if source is not None:
+                self._run_source[pos] = source
+            else:
+                self._run_binding[pos] = bind((pos,), req)
 
         # -- the memory budget, before anything is uploaded -----------------------------------
         stored = None
@@ -145,15 +157,15 @@ class Engine:
         del tensors
 
         # -- cache ----------------------------------------------------------------------------------
-        for pos, shape in state_shapes.items():
-            self._run_state[pos] = torch.zeros(shape, dtype=torch.float32, device=self.device)
+        for key, shape in state_shapes.items():
+            self._run_state[key] = torch.zeros(shape, dtype=torch.float32, device=self.device)
         self.cache = CacheManager(group_specs, page_tokens, num_pages, max_requests)
         self.pools = []
         for gs in group_specs:
             k_el, v_el = gs.page_elements(page_tokens)
-            head = (len(gs.layers), num_pages, gs.num_kv_heads, page_tokens)
+            head = (len(gs.layers), num_pages, gs.num_kv_heads, gs.page_rows(page_tokens))
             k_pool = torch.zeros(head + (gs.head_dim,), dtype=gs.dtype, device=self.device)
-            v_pool = torch.zeros(head + (v_el // (gs.num_kv_heads * page_tokens),), dtype=gs.dtype,
+            v_pool = torch.zeros(head + (v_el // (gs.num_kv_heads * gs.page_rows(page_tokens)),), dtype=gs.dtype,
                                  device=self.device) if v_el else None
             self.pools.append((k_pool, v_pool))
         self.slot_records = SlotRecords(max_requests, self.device)
@@ -255,16 +267,23 @@ class Engine:
         return ctx
 
     def _attach_caches(self, ctx: StepContext) -> None:
+        def view(binding, writes):
+            if binding is None:
+                return None
+            if binding[0] == "bundle":
+                return BundleView((name, view(member, writes)) for name, member in binding[1].items())
+            if binding[0] == "paged":
+                _, gid, k, per_row = binding
+                kp, vp = self.pools[gid]
+                return PagedCacheView(kp[k], None if vp is None else vp[k], ctx.block_tables[gid],
+                                      self.page_tokens, writes, per_row)
+            return StateView(self._run_state[binding[1]], writes)
+
         for pos in range(len(self.spec.run_order)):
             src = self._run_source.get(pos, pos)
-            writes = pos not in self._run_source
-            if src in self._run_group:
-                gid, k = self._run_group[src]
-                kp, vp = self.pools[gid]
-                ctx.layer_caches[pos] = PagedCacheView(kp[k], None if vp is None else vp[k], ctx.block_tables[gid],
-                                                       self.page_tokens, writes)
-            elif src in self._run_state:
-                ctx.layer_caches[pos] = StateView(self._run_state[src], writes)
+            cache = view(self._run_binding.get(src), pos not in self._run_source)
+            if cache is not None:
+                ctx.layer_caches[pos] = cache
 
     def step(self, entries: Sequence, check: bool = True) -> Optional[torch.Tensor]:
         """Run one batch.  ``entries``: ``StepEntry`` or ``(rid, tokens, want)`` tuples.

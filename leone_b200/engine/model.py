@@ -17,7 +17,7 @@ import torch
 from .. import parts as _parts  # noqa: F401  (registers built-in parts)
 from ..parts.base import FixedState, PagedKV, Runtime, WeightSpec
 from ..parts.spec import ModelSpec
-from ..registry import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, POSITION_ENCODINGS,
+from ..registry import (BLOCKS, CONVS, EMBEDDINGS, FEED_FORWARDS, HEADS, INJECTIONS, MIXERS, NORMS, POSITION_ENCODINGS,
                         spec_from_config)
 
 
@@ -63,7 +63,7 @@ class Model:
                     return None
                 if registry == "mixer":
                     return _build_mixer(part_spec, rt, self.position_encodings)
-                table = {"feed_forward": FEED_FORWARDS, "norm": NORMS}.get(registry)
+                table = {"feed_forward": FEED_FORWARDS, "norm": NORMS, "conv": CONVS}.get(registry)
                 if table is None:
                     raise ValueError(f"layer {layer.prefix}: no registry '{registry}' for an extra part")
                 return table.get(part_spec.kind)(dict(part_spec.params), rt)
@@ -132,7 +132,7 @@ class Model:
         """Per position of ``run_order``: ``(request, source)``.
 
         A layer that is run twice shares its weights, not its cache: every occurrence in the
-        run order owns a cache of its own (``request`` is a ``PagedKV``/``FixedState``,
+        run order owns a cache of its own (``request`` is a ``PagedKV``/``FixedState``/``CacheBundle``,
         ``source`` is ``None``).  A layer with ``cache_of`` owns none and reads the cache of
         the latest earlier occurrence of that layer (``request`` is ``None``, ``source`` its
         run position)."""
@@ -141,7 +141,7 @@ class Model:
         for pos, idx in enumerate(self.spec.run_order):
             layer = self.spec.layers[idx]
             if layer.cache_of is None:
-                plan.append((self.blocks[idx].mixer.cache_request(), None))
+                plan.append((self.blocks[idx].cache_request(), None))
                 latest[idx] = pos
             else:
                 plan.append((None, latest[layer.cache_of]))

@@ -617,24 +617,188 @@ class CudaOps:
             cache.page_tokens, kp.shape[0], bt.shape[0], _ptr(ctx.status), self._stream()), "attention_latent")
 
     def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False, groups=1,
-                      groups_kept=None, weight_scale=1.0):
+                      groups_kept=None, weight_scale=1.0, bias=None, experts=None):
         """Router logits as an fp32 product (bfloat16 operands multiply exactly in fp32), then the
         scores and the ``top`` best experts of every token (``csrc/experts.cu``), optionally among
         the experts of the ``groups_kept`` best of ``groups`` groups only; the weights times
-        ``weight_scale``."""
+        ``weight_scale``.  ``softmax``: False (sigmoid scores), True (softmax over all experts) or
+        ``"chosen"`` (the logits are ranked, the weights are the softmax over the chosen ones).
+        ``bias``: fp32 ``[experts]`` added to the logits.  ``experts``: the router matrix's first so
+        many rows are experts; further rows are other per-token logits that ride in the same product.
+        Returns the fp32 logits ``[n, rows]`` (valid until the next call)."""
         n, width = x.shape
         if not isinstance(w_router, PreparedMatrix):
             w_router = self.prepare_matrix(w_router)
-        experts = w_router.out_features
+        rows = w_router.out_features
+        experts = rows if experts is None else int(experts)
         _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top
-              and weight.numel() == n * top, "experts_route layout")
-        logits = self._scratch("router_logits", n, experts, torch.float32)
+              and weight.numel() == n * top and 0 < experts <= rows, "experts_route layout")
+        _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == experts),
+              "experts_route bias")
+        logits = self._scratch("router_logits", n, rows, torch.float32)
         self.linear(x, w_router, logits)
         self.launches += 1
-        _check(self.mixers.leone_experts_select(_ptr(logits), logits.stride(0), n, experts, top, 1 if softmax else 0,
+        mode = 2 if softmax == "chosen" else (1 if softmax else 0)
+        _check(self.mixers.leone_experts_select(_ptr(logits), logits.stride(0), _ptr(bias), n, experts, top, mode,
                                                 1 if renormalize else 0, int(groups), int(groups_kept or groups),
                                                 c_float(weight_scale), _ptr(chosen), _ptr(weight), self._stream()),
                "experts_select")
+        return logits
+
+    # -- short convolutions with state, the minGRU recurrence, pooled-window attention --------------
+    def short_conv(self, ctx, x, weight, state, out, add_input=False):
+        """``out_t = (x_t if add_input) + sum_j weight[:, j] x_(t - taps + 1 + j)`` on every channel,
+        inputs before the step from ``state`` (fp32 ``[slots, taps - 1, channels]``), which is not
+        changed (``csrc/short_conv.cu``).  ``weight``: fp32 ``[channels, taps]``."""
+        n, channels = out.shape
+        taps = weight.shape[1]
+        _need(x.shape == (n, channels) and x.stride(1) == 1 and out.stride(1) == 1 and weight.dtype == torch.float32
+              and weight.is_contiguous() and weight.shape[0] == channels, "short_conv layout")
+        _need(taps == 1 or (state.dtype == torch.float32 and state.is_contiguous()
+                            and tuple(state.shape[1:]) == (taps - 1, channels)), "short_conv state")
+        self.launches += 1
+        _check(self.mixers.leone_short_conv(
+            _dt(x.dtype), _dt(out.dtype), _ptr(x), x.stride(0), _ptr(weight), _ptr(state), _ptr(out), out.stride(0),
+            _ptr(ctx.q_start), _ptr(ctx.seq_of_token), _ptr(ctx.slot_ids), n, channels, taps, 1 if add_input else 0,
+            ctx.n_seqs, state.shape[0] if state is not None else 0, _ptr(ctx.status), self._stream()), "short_conv")
+
+    def short_conv_state(self, ctx, x, state):
+        """The state after the step: the last ``taps - 1`` rows of ``x`` of every sequence (older
+        state rows move up where the step brought fewer).  Runs after every reader of the state."""
+        keep, channels = state.shape[1], state.shape[2]
+        _need(x.shape[1] >= channels and x.stride(1) == 1 and state.dtype == torch.float32 and state.is_contiguous(),
+              "short_conv_state layout")
+        if keep == 0:
+            return
+        self.launches += 1
+        _check(self.mixers.leone_short_conv_state(
+            _dt(x.dtype), _ptr(x), x.stride(0), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.slot_ids), ctx.n_seqs,
+            channels, keep + 1, state.shape[0], _ptr(ctx.status), self._stream()), "short_conv_state")
+
+    def min_gru(self, ctx, proj, z_bias, x_bias, state, out, out_scale=1.0, chunk=0):
+        """``S_t = (1 - z) S_(t-1) + z c`` per channel with ``z = sigmoid(pz + bz)``, ``u = px + bx``,
+        ``c = u + 1/2`` where ``u >= 0`` else ``sigmoid(u)``; ``out_t = out_scale * S_t * silu(pg)``.
+        ``proj``: rows ``[pz | px | pg]``; ``state``: fp32 ``[slots, width]``.  ``chunk`` > 0: the
+        step's tokens are cut into chunks of that many that run side by side."""
+        n, width = out.shape
+        _need(proj.shape == (n, 3 * width) and proj.stride(1) == 1 and out.stride(1) == 1
+              and state.dtype == torch.float32 and state.is_contiguous() and state.shape[1] == width, "min_gru layout")
+        for b in (z_bias, x_bias):
+            _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == width), "min_gru bias")
+        n_chunks, chunk_args = 0, (c_void_p(0),) * 5
+        if chunk > 0:
+            cuts = ctx.__dict__.setdefault("_token_chunks", {})      # the cut is the same for every layer of the step
+            if chunk not in cuts:
+                first, last, seq_start = [], [], [0]
+                for a, q in zip(np.cumsum(ctx.q_lens) - ctx.q_lens, ctx.q_lens):
+                    for c0 in range(0, int(q), chunk):
+                        first.append(int(a) + c0)
+                        last.append(int(a) + min(c0 + chunk, int(q)))
+                    seq_start.append(len(first))
+                cuts[chunk] = (len(first), torch.tensor(first + last + seq_start, dtype=torch.int32).to(self.device))
+            n_chunks, meta = cuts[chunk]
+            sums = self._scratch("min_gru_chunks", 2 * n_chunks, width, torch.float32)
+            chunk_args = (_ptr(meta), _ptr(meta[n_chunks:]), _ptr(meta[2 * n_chunks:]), _ptr(sums), _ptr(sums[n_chunks:]))
+        self.launches += 1 if n_chunks == 0 else 3
+        _check(self.mixers.leone_min_gru(
+            _dt(proj.dtype), _dt(out.dtype), _ptr(proj), proj.stride(0), 0, width, 2 * width, _ptr(z_bias), _ptr(x_bias),
+            _ptr(state), _ptr(out), out.stride(0), _ptr(ctx.q_start), _ptr(ctx.slot_ids), ctx.n_seqs, width,
+            state.shape[0], c_float(out_scale), n_chunks, *chunk_args, _ptr(ctx.status), self._stream()), "min_gru")
+
+    def scale_rows(self, a, gate, scale=1.0):
+        """In place: ``a[t, :] *= scale * sigmoid(gate[t])``; ``gate``: one fp32 logit per row (a
+        column of a wider matrix is fine) or ``None``."""
+        n, cols = a.shape
+        _need(a.stride(1) == 1 and (gate is None or (gate.dtype == torch.float32 and gate.shape[0] == n)), "scale_rows layout")
+        self.launches += 1
+        _check(self.mixers.leone_scale_rows(_dt(a.dtype), _ptr(a), a.stride(0), n, cols, _ptr(gate),
+                                            0 if gate is None else gate.stride(0), c_float(scale), self._stream()),
+               "scale_rows")
+
+    def add_scaled(self, x, y, scale=1.0):
+        """In place: ``x += scale * y`` (both fp32, same shape)."""
+        _need(x.dtype == torch.float32 and y.dtype == torch.float32 and x.shape == y.shape and x.is_contiguous()
+              and y.is_contiguous(), "add_scaled layout")
+        self.launches += 1
+        _check(self.mixers.leone_add_scaled(_ptr(x), _ptr(y), ctypes.c_longlong(x.numel()), c_float(scale),
+                                            self._stream()), "add_scaled")
+
+    def attention_pooled_prepare(self, ctx, proj, q_out, n_q, n_kv, dk, dv, conv_w, conv_state, freqs, pairing,
+                                 magnitude, unit_norm, eps, cache):
+        """Per token, in fp32: the short convolution of the projected row ``[q | k | v]`` (weights
+        fp32 ``[cols, taps]`` or None; earlier inputs from ``conv_state``), the rotation of q and k,
+        the unit RMS norm of every q and k head, q into ``q_out``, k and v into their pages
+        (``csrc/attention_pooled.cu``)."""
+        n = proj.shape[0]
+        cols = (n_q + n_kv) * dk + n_kv * dv
+        _need(proj.stride(1) == 1 and proj.shape[1] == cols and q_out.shape == (n, n_q * dk) and q_out.stride(1) == 1,
+              "attention_pooled_prepare layout")
+        taps = 0
+        if conv_w is not None:
+            taps = conv_w.shape[1]
+            _need(conv_w.dtype == torch.float32 and conv_w.is_contiguous() and conv_w.shape[0] == cols
+                  and (taps == 1 or (conv_state is not None and conv_state.dtype == torch.float32
+                                     and conv_state.is_contiguous() and tuple(conv_state.shape[1:]) == (taps - 1, cols))),
+                  "attention_pooled_prepare convolution")
+        rot = 0
+        if freqs is not None:
+            _need(freqs.dtype == torch.float32 and freqs.is_contiguous() and 2 * freqs.numel() <= dk,
+                  "attention_pooled_prepare frequencies")
+            rot = 2 * freqs.numel()
+        _need(pairing in ("half_split", "adjacent"), f"rotary pairing '{pairing}'")
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        _need(vp is not None and kp.is_contiguous() and vp.is_contiguous() and kp.dtype == q_out.dtype == vp.dtype
+              and kp.shape[1] == n_kv and kp.shape[2] == cache.page_tokens and kp.shape[3] == dk and vp.shape[3] == dv
+              and bt.dtype == torch.int32 and bt.is_contiguous(), "attention_pooled_prepare cache layout")
+        self.launches += 1
+        _check(self.mixers.leone_attention_pooled_prepare(
+            _dt(proj.dtype), _dt(q_out.dtype), _ptr(proj), proj.stride(0), n, n_q, n_kv, dk, dv, _ptr(conv_w), taps,
+            _ptr(conv_state), _ptr(freqs), rot, 1 if pairing == "adjacent" else 0, c_float(magnitude),
+            1 if unit_norm else 0, c_float(eps), _ptr(q_out), q_out.stride(0), _ptr(ctx.positions),
+            _ptr(ctx.seq_of_token), _ptr(ctx.q_start), _ptr(ctx.slot_ids),
+            conv_state.shape[0] if conv_state is not None else 0, _ptr(bt), bt.shape[1], bt.shape[0],
+            _ptr(kp) if cache.writes else c_void_p(0), _ptr(vp) if cache.writes else c_void_p(0), kp.shape[0],
+            cache.page_tokens, _ptr(ctx.status), self._stream()), "attention_pooled_prepare")
+
+    @staticmethod
+    def _pooled_args(tokens, blocks, n_kv, dk, dv, pool):
+        kp, vp, bt = tokens.k_pool, tokens.v_pool, tokens.block_table
+        kb, vb, pt = blocks.k_pool, blocks.v_pool, blocks.block_table
+        rows = kb.shape[2]
+        _need(kp.is_contiguous() and vp.is_contiguous() and kb.is_contiguous() and vb.is_contiguous()
+              and kp.dtype == vp.dtype == kb.dtype == vb.dtype and kp.shape[1] == n_kv == kb.shape[1]
+              and kp.shape[3] == dk == kb.shape[3] and vp.shape[3] == dv == vb.shape[3]
+              and blocks.page_tokens == tokens.page_tokens and blocks.tokens_per_row == pool
+              and rows == -(-tokens.page_tokens // pool) and bt.dtype == torch.int32 and pt.dtype == torch.int32
+              and bt.is_contiguous() and pt.is_contiguous() and bt.shape[0] == pt.shape[0], "pooled attention cache layout")
+        return (_ptr(kp), _ptr(vp), _ptr(bt), bt.shape[1], kp.shape[0], tokens.page_tokens,
+                _ptr(kb), _ptr(vb), _ptr(pt), pt.shape[1], kb.shape[0], rows)
+
+    def attention_pool_blocks(self, ctx, tokens, blocks, n_kv, dk, dv, pool):
+        """Every block of ``pool`` positions that one of the step's tokens ends gets its mean key
+        and mean value (over the rows as the token cache holds them) in the cache of blocks."""
+        args = self._pooled_args(tokens, blocks, n_kv, dk, dv, pool)
+        self.launches += 1
+        _check(self.mixers.leone_attention_pool_blocks(
+            _dt(tokens.k_pool.dtype), *args, _ptr(ctx.positions), _ptr(ctx.seq_of_token), ctx.n_tokens, ctx.n_seqs,
+            n_kv, dk, dv, pool, _ptr(ctx.status), self._stream()), "attention_pool_blocks")
+
+    def attention_pooled(self, ctx, q, out, tokens, blocks, n_q, n_kv, dk, dv, scale, window, pool, out_scale=1.0):
+        """Softmax attention of every token over the last ``window`` cached keys and the mean keys
+        of all blocks of ``pool`` positions that lie wholly before that window; ``out`` times
+        ``out_scale``."""
+        n = q.shape[0]
+        _need(q.shape[1] == n_q * dk and q.stride(1) == 1 and out.shape == (n, n_q * dv) and out.stride(1) == 1
+              and out.dtype == q.dtype == tokens.k_pool.dtype, "attention_pooled layout")
+        args = self._pooled_args(tokens, blocks, n_kv, dk, dv, pool)
+        self.launches += 1
+        if self.fast is not None and hasattr(self.fast, "attention_pooled") and \
+                self.fast.attention_pooled(self, ctx, q, out, args, n_q, n_kv, dk, dv, scale, window, pool, out_scale):
+            return
+        _check(self.mixers.leone_attention_pooled(
+            _dt(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), *args, _ptr(ctx.seq_of_token),
+            _ptr(ctx.positions), n, n_q, n_kv, dk, dv, c_float(scale), int(window), int(pool), c_float(out_scale),
+            ctx.n_seqs, _ptr(ctx.status), self._stream()), "attention_pooled")
 
     def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
         """``hidden += sum over each token's chosen experts``; scratch comes from ``rt``.

@@ -1,6 +1,6 @@
 """Parts a layer is built from.  Importing this package registers the built-in kinds."""
-from . import (attention, block, embedding, experts, head, injection, latent_attention, linear_attention, mlp,  # noqa: F401
-               rms_norm, rotary, swiglu)
+from . import (attention, block, embedding, experts, head, injection, latent_attention, linear_attention, min_gru,  # noqa: F401
+               mlp, pooled_attention, rms_norm, rotary, short_conv, side_by_side, swiglu)
 from .base import (Block, Embedding, FeedForward, FixedState, Head, Mixer, Norm, PagedCacheView, PagedKV, Part,
                    PositionEncoding, Runtime, StateView, WeightSpec)
 from .spec import LayerSpec, ModelSpec, PartSpec

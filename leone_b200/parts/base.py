@@ -30,7 +30,8 @@ Interfaces, by kind:
     ``apply(ctx, q, k)`` on ``[N, heads, head_dim]`` views in place.
 
 ``Block.forward(ctx, cache, hidden) -> None``
-    The arrangement of norm, mixer and feed-forward around the residual stream.
+    The arrangement of norm, mixer and feed-forward around the residual stream.  ``cache`` is what
+    ``Block.cache_request()`` asked for (by default: what its mixer asked for).
 
 ``Embedding.forward(ctx, hidden) -> None`` / ``Head.forward(ctx, x, out) -> None``
     What stands before the first layer (token ids → fp32 residual stream) and after the final
@@ -86,6 +87,12 @@ class PagedKV:
     dtype: Optional[torch.dtype] = None
     lifetime: Optional[str] = None
     tag: str = ""
+    # A cache of summaries: one row for every ``tokens_per_row`` positions (a mean over a block of
+    # tokens, say).  Pages still cover ``page_tokens`` positions and are found through the same kind
+    # of block table; a page holds ``ceil(page_tokens / tokens_per_row)`` rows.  The row of the
+    # summary whose last position is ``e`` lies in the page of ``e`` at ``(e % page_tokens) //
+    # tokens_per_row``.
+    tokens_per_row: int = 1
 
     def resolved(self, run_dtype: torch.dtype) -> "PagedKV":
         lifetime = self.lifetime or ("window" if self.window else "full")
@@ -94,16 +101,30 @@ class PagedKV:
         if lifetime == "window" and not self.window:
             raise ValueError("a paged cache with lifetime 'window' needs a window")
         vd = self.head_dim if self.value_head_dim is None else int(self.value_head_dim)
-        if self.num_kv_heads <= 0 or self.head_dim <= 0 or vd < 0:
+        if self.num_kv_heads <= 0 or self.head_dim <= 0 or vd < 0 or self.tokens_per_row <= 0:
             raise ValueError(f"a paged cache needs positive sizes, got {self}")
         return PagedKV(self.num_kv_heads, self.head_dim, self.window if lifetime == "window" else None,
-                       vd, self.dtype or run_dtype, lifetime, self.tag)
+                       vd, self.dtype or run_dtype, lifetime, self.tag, int(self.tokens_per_row))
 
 
 @dataclass
 class FixedState:
     """A mixer's request for fixed-size per-request state, ``shape`` per request, fp32."""
     shape: Tuple[int, ...]
+
+
+@dataclass
+class CacheBundle:
+    """A request for several caches at once, by name: a part made of parts (two mixers side by
+    side, a block with state of its own beside its mixer's) asks for what each of them needs.
+    A member is a :class:`PagedKV`, a :class:`FixedState`, another bundle or ``None``; the part
+    receives a :class:`BundleView` with a view under every name."""
+    members: Dict[str, object]
+
+
+class BundleView(dict):
+    """``view[name]``: the cache that the bundle's member of that name asked for (``None`` for a
+    member that asked for nothing)."""
 
 
 @dataclass
@@ -114,6 +135,7 @@ class PagedCacheView:
     block_table: torch.Tensor     # int32 [B, max_blocks]; -1 where no page
     page_tokens: int
     writes: bool = True           # False for a layer that borrows another layer's cache
+    tokens_per_row: int = 1       # > 1: a cache of summaries, see PagedKV
 
 
 @dataclass
@@ -344,6 +366,11 @@ class Block:
         self.ffn_norm = ffn_norm
         for name, part in extra.items():
             setattr(self, name, part)
+
+    def cache_request(self):
+        """What a run of this layer keeps per request: the mixer's cache; an arrangement with state
+        of its own returns a :class:`CacheBundle` that holds the mixer's request beside its own."""
+        return self.mixer.cache_request()
 
     def forward(self, ctx, cache, hidden):
         raise NotImplementedError

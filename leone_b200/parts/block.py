@@ -1,8 +1,10 @@
 """Arrangements of norm, mixer and feed-forward around the residual stream."""
 from __future__ import annotations
 
+import torch
+
 from ..registry import BLOCKS
-from .base import Block
+from .base import Block, CacheBundle
 
 
 @BLOCKS.register("pre_norm")
@@ -50,6 +52,46 @@ class PreNormBlock(Block):
         else:
             self.feed_forward.forward(ctx, x, hidden)
         return after if after is not None and after.ready else None
+
+
+@BLOCKS.register("pre_norm_conv")
+class PreNormConvBlock(Block):
+    """``h += mixer(c1(norm(h))); h += ffn(c2(norm(h)))`` where ``c1`` and ``c2`` are convolution parts
+    with state of their own (extra parts ``mixer_conv`` and ``ffn_conv``; either may be missing):
+    what a sublayer reads passes through a short causal convolution over time first.  The norm's
+    rows go to the convolution in fp32 where the norm offers that.  The arrangement keeps the
+    convolutions' state beside the mixer's cache.  A layer without a feed-forward is the first half
+    only."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, mixer_conv=None, ffn_conv=None, **extra):
+        if mixer_norm is None or (feed_forward is None) != (ffn_norm is None) or extra or \
+                (feed_forward is None and ffn_conv is not None):
+            raise ValueError("the pre_norm_conv arrangement is norm, convolution, mixer and, optionally, norm, "
+                             "convolution, feed-forward: it takes exactly those parts")
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm)
+        self.mixer_conv, self.ffn_conv = mixer_conv, ffn_conv
+
+    def cache_request(self):
+        return CacheBundle({"mixer": self.mixer.cache_request(),
+                            "mixer_conv": None if self.mixer_conv is None else self.mixer_conv.cache_request(),
+                            "ffn_conv": None if self.ffn_conv is None else self.ffn_conv.cache_request()})
+
+    @staticmethod
+    def _read(ctx, hidden, norm, conv, cache, tag):
+        if conv is None:
+            return norm.forward(ctx, hidden)
+        try:
+            wide = norm.forward(ctx, hidden, out_name="normed_wide", dtype=torch.float32)
+        except TypeError:                      # a norm that gives the run dtype only
+            wide = norm.forward(ctx, hidden)
+        return conv.forward(ctx, cache, wide, out_name="normed_conv_" + tag)
+
+    def forward(self, ctx, cache, hidden):
+        x = self._read(ctx, hidden, self.mixer_norm, self.mixer_conv, cache["mixer_conv"], "a")
+        self.mixer.forward(ctx, cache["mixer"], x, hidden)
+        if self.feed_forward is not None:
+            x = self._read(ctx, hidden, self.ffn_norm, self.ffn_conv, cache["ffn_conv"], "b")
+            self.feed_forward.forward(ctx, x, hidden)
 
 
 @BLOCKS.register("parallel")

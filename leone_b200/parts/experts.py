@@ -7,6 +7,12 @@ multiplies the expert's input (``scale = "input"``: ``sum expert_e(w_e x)``) or 
 (``"output"``).  An expert is ``W_down (silu(W_gate a) * (W_up a))`` without biases.  An optional
 shared expert of the same form (size ``shared_size``) runs on every token and is added.
 
+``score = "softmax_chosen"``: the logits themselves are ranked and the chosen experts' weights are
+the softmax over the chosen logits only.  ``router_bias_name``: a bias ``[experts]`` added to the
+router logits (fp32).  ``shared_gate_name``: a matrix ``[1, hidden]``; the shared expert's output is
+multiplied by ``sigmoid(w_sg . x)``, one number per token (its logit rides in the router's fp32
+product).  ``out_scale`` multiplies everything the part adds to the residual stream.
+
 Further parameters, each off by default: ``expert_form = "relu_squared"`` makes an expert the
 ungated ``W_down max(W_up a, 0)^2`` (tensors ``up`` and ``down`` only); ``groups`` and
 ``groups_kept`` restrict the choice to the experts of the best groups (the experts form ``groups``
@@ -43,7 +49,11 @@ class RoutedExperts(FeedForward):
         self.groups = int(params.get("groups", 1))
         self.groups_kept = int(params.get("groups_kept", self.groups))
         self.weight_scale = float(params.get("weight_scale", 1.0))
-        if self.score not in ("sigmoid", "softmax") or self.scale not in ("input", "output"):
+        self.out_scale = float(params.get("out_scale", 1.0))
+        self.router_bias_name = params.get("router_bias_name")
+        self.shared_gate_name = params.get("shared_gate_name") if self.shared_ff else None
+        self.router_bias = None
+        if self.score not in ("sigmoid", "softmax", "softmax_chosen") or self.scale not in ("input", "output"):
             raise ValueError(f"routed experts: score '{self.score}' / scale '{self.scale}'")
         if self.form not in ("gated_silu", "relu_squared"):
             raise ValueError(f"routed experts: expert form '{self.form}'")
@@ -75,6 +85,10 @@ class RoutedExperts(FeedForward):
             specs += [WeightSpec(self._expert(e, "up"), (self.ff, self.hidden)),
                       WeightSpec(self._expert(e, "down"), (self.hidden, self.ff))]
         specs.append(WeightSpec(self.router_name, (self.experts, self.hidden)))
+        if self.router_bias_name:
+            specs.append(WeightSpec(self.router_bias_name, (self.experts,), role="vector", std=0.5))
+        if self.shared_gate_name:
+            specs.append(WeightSpec(self.shared_gate_name, (1, self.hidden)))
         if self.shared_ff:
             specs += [WeightSpec(self.shared_pattern.format("gate"), (self.shared_ff, self.hidden)),
                       WeightSpec(self.shared_pattern.format("up"), (self.shared_ff, self.hidden)),
@@ -85,7 +99,12 @@ class RoutedExperts(FeedForward):
         def stack(which):
             return torch.stack([tensors[self._expert(e, which)] for e in range(self.experts)]).contiguous()
         self.w_gate, self.w_up, self.w_down = stack("gate") if self.gated else None, stack("up"), stack("down")
-        self.w_router = self.rt.ops.prepare_matrix(tensors[self.router_name].contiguous())
+        router = tensors[self.router_name]
+        if self.shared_gate_name:           # the gate's logit is one more row of the router's product
+            router = torch.cat([router, tensors[self.shared_gate_name].to(router.dtype)], dim=0)
+        self.w_router = self.rt.ops.prepare_matrix(router.contiguous())
+        if self.router_bias_name:
+            self.router_bias = tensors[self.router_bias_name].float().contiguous()
         if self.shared_ff:
             ops = self.rt.ops
             self.w_shared_gate_up = ops.prepare_gate_up(tensors[self.shared_pattern.format("gate")],
@@ -114,12 +133,19 @@ class RoutedExperts(FeedForward):
         chosen = rt.flat_buffer("experts_chosen", pairs, torch.int32, reserve=rt.max_tokens * self.top)[:pairs]
         weight = rt.flat_buffer("experts_weight", pairs, torch.float32, reserve=rt.max_tokens * self.top)[:pairs]
         extra = {}
-        if self.groups > 1 or self.weight_scale != 1.0:
-            extra = dict(groups=self.groups, groups_kept=self.groups_kept, weight_scale=self.weight_scale)
-        ops.experts_route(x, self.w_router, chosen, weight, self.top, self.score == "softmax", self.renormalize, **extra)
+        scale = self.weight_scale * self.out_scale
+        if self.groups > 1 or scale != 1.0:
+            extra = dict(groups=self.groups, groups_kept=self.groups_kept, weight_scale=scale)
+        if self.router_bias is not None or self.shared_gate_name:
+            extra.update(bias=self.router_bias, experts=self.experts)
+        softmax = "chosen" if self.score == "softmax_chosen" else self.score == "softmax"
+        logits = ops.experts_route(x, self.w_router, chosen, weight, self.top, softmax, self.renormalize, **extra)
         ops.experts_forward(x, self.w_gate, self.w_up, self.w_down, chosen, weight, self.top,
                             self.scale == "input", hidden, rt)
         if self.shared_ff:
             act = rt.buffer("experts_shared_act", n, self.shared_ff, rt.dtype)
             ops.linear_swiglu(x, self.w_shared_gate_up, act)
+            if self.shared_gate_name or self.out_scale != 1.0:
+                gate = logits[:, self.experts:self.experts + 1] if self.shared_gate_name else None
+                ops.scale_rows(act, gate, self.out_scale)
             ops.linear(act, self.w_shared_down, hidden, residual=hidden)

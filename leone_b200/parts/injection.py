@@ -4,6 +4,8 @@
 first), ``x0`` being what the embedding left.  The two halves of ``W`` are kept apart, so that the
 product over ``x0``, which is the same at every place the part runs in a step, is formed once per
 step (fp32) and the product over ``x`` adds it in its epilogue.
+
+``add_origin``: ``x <- x + scale * x0``, no weights: the embedding's rows added to the stream again.
 """
 from __future__ import annotations
 
@@ -53,3 +55,13 @@ class ConcatLinear(Injection):
             self._origin_done = True
         ops.convert(hidden, operand)
         ops.linear(operand, self.w_stream, hidden, residual=const)
+
+
+@INJECTIONS.register("add_origin")
+class AddOrigin(Injection):
+    def __init__(self, params, rt):
+        super().__init__(params, rt)
+        self.scale = float(params.get("scale", 1.0))
+
+    def forward(self, ctx, hidden, origin):
+        self.rt.ops.add_scaled(hidden, origin, self.scale)

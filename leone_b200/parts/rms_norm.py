@@ -36,9 +36,10 @@ class RMSNorm(Norm):
     def defer(self, ctx, hidden, tag="a"):
         return DeferredNorm(self, ctx, hidden, self.weight_f32, self.eps, tag)
 
-    def forward(self, ctx, hidden, rows=None, out_name="normed"):
+    def forward(self, ctx, hidden, rows=None, out_name="normed", dtype=None):
+        """``dtype``: of the result (default: the run dtype; fp32 for a consumer that goes on in fp32)."""
         n = hidden.shape[0] if rows is None else rows.shape[0]
-        out = self.rt.buffer(out_name, n, self.size, self.rt.dtype)
+        out = self.rt.buffer(out_name, n, self.size, dtype or self.rt.dtype)
         self.rt.ops.rms_norm(hidden, self.weight, out, self.eps, rows)
         return out
 

@@ -28,8 +28,9 @@ class LayerSpec:
     ``prefix`` is the layer's tensor-name prefix in the checkpoint.  The feed-forward and either
     norm may be ``None`` for an arrangement that has none (the block then gets ``None`` in its
     place); ``extra`` holds further named parts of the arrangement, each as ``(registry, spec)``
-    with ``registry`` one of ``"mixer"``, ``"feed_forward"``, ``"norm"`` (a second norm after the
-    mixer, a parallel branch), given to the block as keyword arguments.
+    with ``registry`` one of ``"mixer"``, ``"feed_forward"``, ``"norm"``, ``"conv"`` (a second norm
+    after the mixer, a parallel branch, a convolution in front of a sublayer), given to the block as
+    keyword arguments.
     ``cache_of`` names another layer whose cache this layer's mixer reads
     instead of owning one (it then writes nothing).  A layer named twice in the
     run order shares its weights between the runs; each run owns its own cache.

@@ -54,6 +54,7 @@ BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
 INJECTIONS = Registry("injection")
+CONVS = Registry("convolution")
 
 
 class ArchitectureEntry:

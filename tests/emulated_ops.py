@@ -273,8 +273,16 @@ class EmulatedOps:
         out.copy_(res.reshape(n, heads * dv).to(out.dtype))
 
     def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False, groups=1,
-                      groups_kept=None, weight_scale=1.0):
-        z = x.float() @ w_router.float().t()
+                      groups_kept=None, weight_scale=1.0, bias=None, experts=None):
+        logits = x.float() @ w_router.float().t()
+        z = logits if experts is None else logits[:, :experts]
+        if bias is not None:
+            z = z + bias
+        if softmax == "chosen":
+            val, idx = torch.topk(z, top, dim=-1)
+            chosen.copy_(idx.reshape(-1).to(torch.int32))
+            weight.copy_(torch.softmax(val, dim=-1).reshape(-1) * weight_scale)
+            return logits
         s = torch.softmax(z, dim=-1) if softmax else torch.sigmoid(z)
         if groups > 1 and (groups_kept or groups) < groups:
             worth = s.view(s.shape[0], groups, -1).max(dim=-1).values
@@ -285,6 +293,112 @@ class EmulatedOps:
             val = val / val.sum(dim=-1, keepdim=True)
         chosen.copy_(idx.reshape(-1).to(torch.int32))
         weight.copy_(val.reshape(-1) * weight_scale)
+        return logits
+
+    # -- short convolutions with state, the minGRU recurrence, pooled-window attention --------------
+    @staticmethod
+    def _conv_rows(ctx, x, weight, state, add_input):
+        """fp32 rows after the convolution; inputs before the step come from the state."""
+        x = x.float()
+        taps = weight.shape[1]
+        out = torch.zeros_like(x)
+        bounds, slots = ctx.q_start.tolist(), ctx.slot_ids.tolist()
+        for s, slot in enumerate(slots):
+            a, b = bounds[s], bounds[s + 1]
+            hist = x[a:b] if taps == 1 else torch.cat([state[slot].float(), x[a:b]], dim=0)
+            for t in range(b - a):
+                out[a + t] = (weight.t() * hist[t:t + taps]).sum(dim=0)
+        return out + x if add_input else out
+
+    def short_conv(self, ctx, x, weight, state, out, add_input=False):
+        out.copy_(self._conv_rows(ctx, x, weight, state, add_input).to(out.dtype))
+
+    def short_conv_state(self, ctx, x, state):
+        keep, channels = state.shape[1], state.shape[2]
+        bounds, slots = ctx.q_start.tolist(), ctx.slot_ids.tolist()
+        for s, slot in enumerate(slots):
+            hist = torch.cat([state[slot], x[bounds[s]:bounds[s + 1], :channels].float()], dim=0)
+            state[slot] = hist[hist.shape[0] - keep:]
+
+    def min_gru(self, ctx, proj, z_bias, x_bias, state, out, out_scale=1.0, chunk=0):
+        width = out.shape[1]
+        p = proj.float()
+        z = torch.sigmoid(p[:, :width] + (0 if z_bias is None else z_bias))
+        u = p[:, width:2 * width] + (0 if x_bias is None else x_bias)
+        cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+        g = p[:, 2 * width:]
+        bounds, slots = ctx.q_start.tolist(), ctx.slot_ids.tolist()
+        for s, slot in enumerate(slots):
+            st = state[slot]
+            for t in range(bounds[s], bounds[s + 1]):
+                st = (1.0 - z[t]) * st + z[t] * cand[t]
+                out[t] = (out_scale * st * g[t] * torch.sigmoid(g[t])).to(out.dtype)
+            state[slot] = st
+
+    def scale_rows(self, a, gate, scale=1.0):
+        f = scale if gate is None else scale * torch.sigmoid(gate.float().reshape(-1, 1))
+        a.copy_((a.float() * f).to(a.dtype))
+
+    def add_scaled(self, x, y, scale=1.0):
+        x.add_(y, alpha=scale)
+
+    def attention_pooled_prepare(self, ctx, proj, q_out, n_q, n_kv, dk, dv, conv_w, conv_state, freqs, pairing,
+                                 magnitude, unit_norm, eps, cache):
+        n = proj.shape[0]
+        x = proj.float() if conv_w is None else self._conv_rows(ctx, proj, conv_w, conv_state, False)
+        q, k = x[:, :n_q * dk].reshape(n, n_q, dk), x[:, n_q * dk:(n_q + n_kv) * dk].reshape(n, n_kv, dk)
+        v = x[:, (n_q + n_kv) * dk:].reshape(n, n_kv, dv)
+        pos = ctx.positions.long()
+        q, k = self._rotate(q, pos, freqs, magnitude, pairing), self._rotate(k, pos, freqs, magnitude, pairing)
+        if unit_norm:
+            q = q * torch.rsqrt((q * q).mean(dim=-1, keepdim=True) + eps)
+            k = k * torch.rsqrt((k * k).mean(dim=-1, keepdim=True) + eps)
+        q_out.copy_(q.reshape(n, -1).to(q_out.dtype))
+        if not cache.writes:
+            return
+        pt = cache.page_tokens
+        page = cache.block_table[ctx.seq_of_token.long(), pos // pt].long()
+        assert (page >= 0).all(), "write into a block without a page"
+        cache.k_pool[page, :, pos % pt, :] = k.to(cache.k_pool.dtype)
+        cache.v_pool[page, :, pos % pt, :] = v.to(cache.v_pool.dtype)
+
+    def attention_pool_blocks(self, ctx, tokens, blocks, n_kv, dk, dv, pool):
+        pt = tokens.page_tokens
+        for p, s in zip(ctx.positions.tolist(), ctx.seq_of_token.tolist()):
+            if (p + 1) % pool:
+                continue
+            idx = torch.arange(p - pool + 1, p + 1)
+            pages = tokens.block_table[s, idx // pt].long()
+            assert (pages >= 0).all(), "a block's token was given back before the block was complete"
+            dst = int(blocks.block_table[s, p // pt])
+            assert dst >= 0
+            row = (p % pt) // pool
+            blocks.k_pool[dst, :, row, :] = tokens.k_pool[pages, :, idx % pt, :].float().mean(dim=0).to(blocks.k_pool.dtype)
+            blocks.v_pool[dst, :, row, :] = tokens.v_pool[pages, :, idx % pt, :].float().mean(dim=0).to(blocks.v_pool.dtype)
+
+    def attention_pooled(self, ctx, q, out, tokens, blocks, n_q, n_kv, dk, dv, scale, window, pool, out_scale=1.0):
+        n = q.shape[0]
+        qf = q.float().view(n, n_q, dk)
+        g = n_q // n_kv
+        pt = tokens.page_tokens
+        res = torch.zeros(n, n_q, dv)
+        for t, (p, s) in enumerate(zip(ctx.positions.tolist(), ctx.seq_of_token.tolist())):
+            idx = torch.arange(max(0, p - window + 1), p + 1)
+            pages = tokens.block_table[s, idx // pt].long()
+            assert (pages >= 0).all(), "read from a block without a page"
+            keys, vals = tokens.k_pool[pages, :, idx % pt, :].float(), tokens.v_pool[pages, :, idx % pt, :].float()
+            seen = max(0, (p - window + 1) // pool)
+            if seen:
+                ends = torch.arange(seen) * pool + pool - 1
+                bp = blocks.block_table[s, ends // pt].long()
+                assert (bp >= 0).all()
+                rows = (ends % pt) // pool
+                keys = torch.cat([blocks.k_pool[bp, :, rows, :].float(), keys])
+                vals = torch.cat([blocks.v_pool[bp, :, rows, :].float(), vals])
+            for h in range(n_q):
+                w = torch.softmax((keys[:, h // g, :] @ qf[t, h]) * scale, dim=0)
+                res[t, h] = (w[:, None] * vals[:, h // g, :]).sum(0)
+        out.copy_((res * out_scale).reshape(n, n_q * dv).to(out.dtype))
 
     def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
         n = x.shape[0]
