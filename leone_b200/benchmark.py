@@ -415,6 +415,43 @@ def _malapel_shape(width: int, runs: int, heads: int, experts: int, top: int, ex
             "loop": {"start": 0, "stop": 2, "times": 2}, "layers": out}
 
 
+def _sakinex_shape(width: int, runs: int, heads: int, experts: int, top: int, expert_ff: int, shared_ff: int,
+                   window: int, pool: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's: every layer the attention over a window and pooled blocks
+    beside a minGRU as wide as the model, four query heads to a key/value head, convolutions of four taps
+    on q, k and v and in front of both sublayers, routed experts with a gated shared expert; the first two
+    layers run twice, so ``runs`` layer runs need ``runs - 2`` layers."""
+    mixer = {"left": {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                      "conv": 4, "mask": {"size": window, "pool": pool},
+                      "rot": {"base": 1000000.0, "dims": 128,
+                              "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+             "right": {"width": width}, "left_scale": 1.0, "right_scale": 1.0}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff}, "router": {"experts": experts, "top": top},
+           "shared": {"ff": shared_ff}}
+    return {"architecture": "Sakinex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5,
+            "canon": {"taps": 4}, "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": moe} for _ in range(runs - 2)]}
+
+
+def _malapel_like_sakinex(width: int, runs: int, heads: int, experts: int, top: int, expert_ff: int, window: int,
+                          vocab: int) -> dict:
+    """The closest existing design at equal size: looped pre-norm layers, every mixer the attention over a
+    sliding window with four query heads to a key/value head, every feed-forward the routed experts."""
+    m = {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+         "rot": {"base": 1000000.0, "dims": 128}, "mask": {"size": window}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff},
+           "router": {"experts": experts, "top": top, "scale": 1.0, "groups": {"count": 1, "keep": 1}}}
+    return {"architecture": "Malapel", "vocab": vocab, "width": width, "norm": {"eps": 1e-6},
+            "loop": {"start": 0, "stop": 2, "times": 2},
+            "layers": [{"type": "attention_3", "mixer": m, "mlp": moe} for _ in range(runs - 2)]}
+
+
+SAKINEX_SIZES = {
+    # name: (width, layer runs, heads, experts, top, expert ff, shared ff, window, pool, vocab)
+    "small": (2048, 8, 16, 32, 4, 768, 1024, 1024, 64, 32768),
+    "medium": (4096, 8, 32, 64, 8, 1024, 2048, 2048, 64, 65536),
+}
+
 MALAPEL_SIZES = {
     # name: (width, layer runs, heads, experts, top, expert ff, window, chunk, vocab)
     "small": (2048, 8, 16, 32, 4, 768, 1024, 1024, 32768),
@@ -440,7 +477,8 @@ class _OpTimer:
         names = ["linear", "linear_swiglu", "rms_norm", "rms_norm_pair", "relu_squared", "linear_per_head",
                  "linear_attention", "gate_norm", "latent_prepare", "attention_latent", "experts_route",
                  "experts_forward", "attention", "qk_norm_rope_write", "embedding", "logit_post", "attention_prepare",
-                 "attention_masked", "convert"]
+                 "attention_masked", "convert", "short_conv", "short_conv_state", "min_gru", "scale_rows", "add_scaled",
+                 "attention_pooled_prepare", "attention_pool_blocks", "attention_pooled"]
         for name in names:
             fn = getattr(self.ops, name, None)
             if fn is None:
@@ -518,6 +556,10 @@ def compare_designs(design: str = "sarizen", size: str = "small", steps: int = 6
     elif design == "sarizen":
         width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab = DESIGN_SIZES[size]
         raw = _sarizen_shape(width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab)
+    elif design == "sakinex":
+        width, layers, heads, experts, top, expert_ff, shared_ff, window, pool, vocab = SAKINEX_SIZES[size]
+        raw = _sakinex_shape(width, layers, heads, experts, top, expert_ff, shared_ff, window, pool, vocab)
+        rank = 0
     else:
         raise ValueError(f"unknown design '{design}'")
     dense = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=width,
@@ -531,7 +573,10 @@ def compare_designs(design: str = "sarizen", size: str = "small", steps: int = 6
                          "expert_ff": expert_ff, "shared_ff": shared_ff, "kv_rank": rank, "window": window,
                          "vocab": vocab, "batch": batch, "context": context, "prefill_tokens": prefill_tokens},
               "peaks": measured_peaks()}
-    for name, cfg in ((design, raw), ("qwen3", dense)):
+    others = [("qwen3", dense)]
+    if design == "sakinex":     # its closest existing model is the looped design with windows and routed experts
+        others.insert(0, ("malapel", _malapel_like_sakinex(width, layers, heads, experts, top, expert_ff, window, vocab)))
+    for name, cfg in [(design, raw)] + others:
         config = config_from_dict(cfg)
         engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_tokens=16,
                                     max_tokens=batch * (context + 4 * steps + warmup + 192) + prefill_tokens,

@@ -42,11 +42,10 @@ def causal_conv(u, w):
     """``u``: [T, C]; ``w``: [C, taps].  ``y_t = sum_j w[:, j] u_(t - taps + 1 + j)``, zeros before t = 0."""
     T, taps = u.shape[0], w.shape[1]
     y = torch.zeros_like(u)
-    for t in range(T):
-        for j in range(taps):
-            s = t - taps + 1 + j
-            if s >= 0:
-                y[t] += w[:, j] * u[s]
+    for j in range(taps):
+        back = taps - 1 - j                  # tap j reads the input `back` positions earlier
+        if back < T:
+            y[back:] += w[:, j] * u[:T - back]
     return y
 
 
@@ -224,3 +223,20 @@ def forward(config, tensors, tokens, dtype=DT, cache_round=None, streams=None):
         if streams is not None:
             streams.append(x.clone())
     return linear(rms(x, eps) * t["final.norm"], t["head"])
+
+
+class PlainSakinex:
+    def __init__(self, cfg, tensors, dtype=DT, cache_round=None):
+        self.cfg, self.tensors, self.dtype, self.cache_round = cfg, tensors, dtype, cache_round
+        self._memo = {}
+
+    def logits(self, tokens):
+        key = tuple(tokens)
+        if key not in self._memo:
+            self._memo[key] = forward(self.cfg, self.tensors, list(tokens), self.dtype, self.cache_round)
+        return self._memo[key]
+
+    def residuals(self, tokens):
+        streams = []
+        forward(self.cfg, self.tensors, list(tokens), self.dtype, self.cache_round, streams)
+        return torch.stack(streams)

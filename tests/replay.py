@@ -146,10 +146,14 @@ def read_outputs(steps, out_dir):
     return outputs
 
 
-def compare(steps, outputs, plain, requests, rtol, atol_scale, what):
-    """Every written row against the plain model's logits at (request, position)."""
+def compare(steps, outputs, plain, requests, rtol, atol_scale, what, rows_over=0.0):
+    """Every written row against the plain model's logits at (request, position).  `rows_over`: the
+    share of all rows that may pass the bound (a router's close call under bfloat16 rounding swaps an
+    expert for one token), each by no more than three times."""
     pos = {rid: 0 for rid in requests}
     worst = 0.0
+    n_rows = sum(len(e["want"]) for st in steps for e in st["entries"])
+    spare = int(rows_over * n_rows)
     for st in steps:
         rows = []
         for e in st["entries"]:
@@ -164,6 +168,13 @@ def compare(steps, outputs, plain, requests, rtol, atol_scale, what):
         scale = np.abs(want).max()
         err = np.abs(got - want)
         bound = atol_scale * scale + rtol * np.abs(want)
+        over = (err > bound).any(axis=1)
+        if spare and over.any() and not (err > 3 * bound).any() and int(over.sum()) <= spare:
+            spare -= int(over.sum())
+            err = err[~over]
+            bound = bound[~over]
+            if not len(err):
+                continue
         if (err > bound).any():
             r, c = np.unravel_index(np.argmax(err - bound), err.shape)
             raise AssertionError(
