@@ -1,6 +1,13 @@
 // The attention of attention_masked.cu on tensor cores (bfloat16, mma.sync m16n8k16, fp32 sums):
-// masks causal / window / chunk, weights softmax / softmax with a silent member of score 0 /
-// sigmoid with a bias per head, keys of dk and values of dv elements (multiples of 16 up to 128).
+// masks causal / window / chunk / window with pooled blocks before it, weights softmax / softmax with
+// a silent member of score 0 / sigmoid with a bias per head, keys of dk and values of dv elements
+// (multiples of 16 up to 128).
+//
+// Window with pooled blocks (mask 3, the rule of attention_pooled.cu): the query at position p sees
+// the keys j with 0 <= p - j < size and the first floor((p - size + 1) / pool) rows of a second cache
+// that holds one mean key and mean value per block of `pool` positions.  The walk over key tiles has
+// two parts, tiles of block rows first and tiles of token rows after them; both feed the same running
+// maximum, denominator and sums, so blocks and tokens share one softmax.
 //
 // Rows of a tile are (token, query head of the KV head's group) pairs of one sequence and one KV
 // head; a warp owns 16 rows.  S = Q K^T and O += P V are MMAs with Q, a tile of 64 keys and the
@@ -43,9 +50,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 constexpr float kLog2e = 1.4426950408889634f;
 __device__ __forceinline__ int mm_first_seen(int mask, int size, int pos) {
-  if (mask == 1) return max(0, pos - size + 1);
+  if (mask == 1 || mask == 3) return max(0, pos - size + 1);
   if (mask == 2) return (pos / size) * size;
   return 0;
+}
+
+// block rows the query at `pos` sees (mask 3 only): the blocks that lie wholly before its window
+__device__ __forceinline__ int mm_blocks_seen(int mask, int size, int pool, int pos) {
+  return mask == 3 && pos - size + 1 >= pool ? (pos - size + 1) / pool : 0;
 }
 
 struct MaskedArgs {
@@ -67,13 +79,45 @@ struct MaskedArgs {
   int splits;
   float* partial;          // decode form with splits > 1: [seq][kv head][split][16][dv + 2]
   int* status;
+  // mask 3: the cache of block means.  The page of a block's last position e (found through
+  // pool_table like a token's page) holds its row at (e % page_tokens) / pool; a page has pool_rows rows.
+  const __nv_bfloat16* kb_pool = nullptr;
+  const __nv_bfloat16* vb_pool = nullptr;
+  const int* pool_table = nullptr;
+  int pool_table_width = 0, pool_pages = 0, pool_rows = 0, pool = 0;
+  float out_scale = 1.f;  // the output rows are multiplied by this
 };
 
+// The place of member j of (sequence, kv head) in its pool, in rows: token j, or block j with `blocks`.
+// -1 and a status word if the table has no page for it.
+__device__ __forceinline__ long long mm_member_slot(const MaskedArgs& a, bool blocks, int seq, int kvh, int j, int tok_row) {
+  if (blocks) {
+    const int e = j * a.pool + a.pool - 1;
+    const int blk = e / a.page_tokens;
+    const int page = blk < a.pool_table_width ? a.pool_table[(size_t)seq * a.pool_table_width + blk] : -1;
+    if (page < 0 || page >= a.pool_pages) {
+      set_status(a.status, kBadPage, tok_row, page, e);
+      return -1;
+    }
+    return ((long long)page * a.n_kv + kvh) * a.pool_rows + (e - blk * a.page_tokens) / a.pool;
+  }
+  const int blk = j / a.page_tokens;
+  const int page = blk < a.table_width ? a.block_table[(size_t)seq * a.table_width + blk] : -1;
+  if (page < 0 || page >= a.num_pages) {
+    set_status(a.status, kBadPage, tok_row, page, j);
+    return -1;
+  }
+  return ((long long)page * a.n_kv + kvh) * a.page_tokens + (j - blk * a.page_tokens);
+}
+
 // Copies keys j0 .. j0 + keys - 1 of (sequence, kv head) into a tile: K rows of dk, V rows of dv elements.
-// Keys outside [lo, hi] become zeros.  `lanes` threads take part, this one is `me`.
+// Keys outside [lo, hi] become zeros.  `lanes` threads take part, this one is `me`.  With `blocks` the
+// members are rows of the cache of block means.
 __device__ __forceinline__ void load_kv_tile(const MaskedArgs& a, int seq, int kvh, int j0, int lo, int hi,
                                              uint32_t k_s, uint32_t v_s, int pitch_k, int pitch_v, int me, int lanes,
-                                             int tok_row, int keys) {
+                                             int tok_row, int keys, bool blocks = false) {
+  const __nv_bfloat16* k_src = blocks ? a.kb_pool : a.k_pool;
+  const __nv_bfloat16* v_src = blocks ? a.vb_pool : a.v_pool;
   const int kc = a.dk >> 3, vc = a.dv >> 3;         // 16-byte chunks per row
   // a block's threads pair up on a key row, a warp's lanes take whole rows: one look-up of the
   // row's page per thread, then copies that depend on nothing else
@@ -83,20 +127,17 @@ __device__ __forceinline__ void load_kv_tile(const MaskedArgs& a, int seq, int k
     bool ok = j >= lo && j <= hi;
     long long slot = 0;
     if (ok) {
-      const int blk = j / a.page_tokens;
-      const int page = blk < a.table_width ? a.block_table[(size_t)seq * a.table_width + blk] : -1;
-      if (page < 0 || page >= a.num_pages) {
-        set_status(a.status, kBadPage, tok_row, page, j);
+      slot = mm_member_slot(a, blocks, seq, kvh, j, tok_row);
+      if (slot < 0) {
         ok = false;
-      } else {
-        slot = ((long long)page * a.n_kv + kvh) * a.page_tokens + (j - blk * a.page_tokens);
+        slot = 0;
       }
     }
-    const __nv_bfloat16* ks = a.k_pool + slot * a.dk;
-    const __nv_bfloat16* vs = a.v_pool + slot * a.dv;
+    const __nv_bfloat16* ks = k_src + slot * a.dk;
+    const __nv_bfloat16* vs = v_src + slot * a.dv;
     const uint32_t kd = k_s + r * pitch_k * 2, vd = v_s + r * pitch_v * 2;
-    for (int w = sub; w < kc; w += tpr) cp_async16_zfill(kd + w * 16, ok ? (const void*)(ks + w * 8) : (const void*)a.k_pool, ok);
-    for (int w = sub; w < vc; w += tpr) cp_async16_zfill(vd + w * 16, ok ? (const void*)(vs + w * 8) : (const void*)a.v_pool, ok);
+    for (int w = sub; w < kc; w += tpr) cp_async16_zfill(kd + w * 16, ok ? (const void*)(ks + w * 8) : (const void*)k_src, ok);
+    for (int w = sub; w < vc; w += tpr) cp_async16_zfill(vd + w * 16, ok ? (const void*)(vs + w * 8) : (const void*)v_src, ok);
   }
 }
 
@@ -106,18 +147,11 @@ __device__ __forceinline__ void load_kv_tile(const MaskedArgs& a, int seq, int k
 // covers whole rows instead of a piece of 32 different ones.
 __device__ __forceinline__ void load_kv_tile_warp(const MaskedArgs& a, int seq, int kvh, int j0, int lo, int hi,
                                                   uint32_t k_s, uint32_t v_s, int pitch_k, int pitch_v, int lane,
-                                                  int tok_row, int keys, long long* slot_s) {
+                                                  int tok_row, int keys, long long* slot_s, bool blocks = false) {
   {
     const int j = j0 + lane;
     long long slot = -1;
-    if (lane < keys && j >= lo && j <= hi) {
-      const int blk = j / a.page_tokens;
-      const int page = blk < a.table_width ? a.block_table[(size_t)seq * a.table_width + blk] : -1;
-      if (page < 0 || page >= a.num_pages)
-        set_status(a.status, kBadPage, tok_row, page, j);
-      else
-        slot = ((long long)page * a.n_kv + kvh) * a.page_tokens + (j - blk * a.page_tokens);
-    }
+    if (lane < keys && j >= lo && j <= hi) slot = mm_member_slot(a, blocks, seq, kvh, j, tok_row);
     __syncwarp();                  // the last tile's readers of slot_s are done
     slot_s[lane] = slot;
     __syncwarp();
@@ -138,8 +172,8 @@ __device__ __forceinline__ void load_kv_tile_warp(const MaskedArgs& a, int seq, 
       }
     }
   };
-  copy(a.k_pool, a.dk, k_s, pitch_k);
-  copy(a.v_pool, a.dv, v_s, pitch_v);
+  copy(blocks ? a.kb_pool : a.k_pool, a.dk, k_s, pitch_k);
+  copy(blocks ? a.vb_pool : a.v_pool, a.dv, v_s, pitch_v);
 }
 
 // One warp, 16 rows, one tile of NT * 8 keys (64 in the prompt form, 32 in the decode form): scores,
@@ -278,13 +312,23 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
   }
   const int pos_first = start + tok0, pos_last = start + tok0 + n_tok - 1;
   const int k_lo = mm_first_seen(a.mask, a.mask_size, pos_first);
-  const int n_tiles = (pos_last - k_lo) / kMmKeys + 1;
-  load_kv_tile(a, seq, kvh, k_lo, k_lo, pos_last, kv_s, kv_s + kMmKeys * pitch_k * 2, pitch_k, pitch_v, tid, kMmThreads,
-               row0 + tok0, kMmKeys);
+  // tiles of block rows (mask 3: the blocks the tile's last token sees) come before the tiles of token rows
+  const int nb_last = mm_blocks_seen(a.mask, a.mask_size, a.pool, pos_last);
+  const int nbt = (nb_last + kMmKeys - 1) / kMmKeys;
+  const int n_tiles = nbt + (pos_last - k_lo) / kMmKeys + 1;
+  auto load_tile = [&](int t, uint32_t dst) {
+    if (t < nbt)
+      load_kv_tile(a, seq, kvh, t * kMmKeys, 0, nb_last - 1, dst, dst + kMmKeys * pitch_k * 2, pitch_k, pitch_v, tid,
+                   kMmThreads, row0 + tok0, kMmKeys, true);
+    else
+      load_kv_tile(a, seq, kvh, k_lo + (t - nbt) * kMmKeys, k_lo, pos_last, dst, dst + kMmKeys * pitch_k * 2, pitch_k,
+                   pitch_v, tid, kMmThreads, row0 + tok0, kMmKeys);
+  };
+  load_tile(0, kv_s);
   asm volatile("cp.async.commit_group;" ::: "memory");
 
   // this thread's two rows
-  int lo_r[2], hi_r[2];
+  int lo_r[2], hi_r[2], blo_r[2] = {0, 0}, bhi_r[2];
   float bias_r[2];
   const int gq = lane >> 2;
 #pragma unroll
@@ -295,6 +339,7 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
     const int pos = start + tok0 + tl;
     hi_r[h] = ok ? pos : -1;
     lo_r[h] = ok ? mm_first_seen(a.mask, a.mask_size, pos) : 0;
+    bhi_r[h] = ok ? mm_blocks_seen(a.mask, a.mask_size, a.pool, pos) - 1 : -1;
     bias_r[h] = (a.weights == 2 && ok) ? a.bias[kvh * g + hg] * kLog2e : 0.f;
   }
   // the warp's rows: the tokens they belong to, for tiles that every row sees in full
@@ -302,6 +347,9 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
   const bool w_all_valid = (warp * 16 + 15) / g < n_tok;
   const int w_lo_max = mm_first_seen(a.mask, a.mask_size, start + tok0 + max(w_tok_last, 0));
   const int w_hi_min = start + tok0 + w_tok_first;
+  // block rows: those the warp's last token sees, and those all its rows see
+  const int w_nb_any = mm_blocks_seen(a.mask, a.mask_size, a.pool, start + tok0 + max(w_tok_last, 0));
+  const int w_nb_all = mm_blocks_seen(a.mask, a.mask_size, a.pool, start + tok0 + w_tok_first);
   float m_run[2], l_run[2];
   // the silent member: maximum 0 and, in one of the four lanes that share a row, denominator 1
   m_run[0] = m_run[1] = a.weights == 1 ? 0.f : -INFINITY;
@@ -312,13 +360,20 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
 
   for (int t = 0; t < n_tiles; ++t) {
     const uint32_t cur = kv_s + (t & 1) * stage_bytes, nxt = kv_s + ((t + 1) & 1) * stage_bytes;
-    if (t + 1 < n_tiles)
-      load_kv_tile(a, seq, kvh, k_lo + (t + 1) * kMmKeys, k_lo, pos_last, nxt, nxt + kMmKeys * pitch_k * 2, pitch_k,
-                   pitch_v, tid, kMmThreads, row0 + tok0, kMmKeys);
+    if (t + 1 < n_tiles) load_tile(t + 1, nxt);
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 1;" ::: "memory");
     __syncthreads();
-    const int j0 = k_lo + t * kMmKeys;
+    if (t < nbt) {
+      const int b0 = t * kMmKeys;
+      if ((warp * 16) / g < n_tok && b0 < w_nb_any)
+        tile_step<DKT, DVT, 8>(q_s + warp * 16 * pitch_k * 2, cur, cur + kMmKeys * pitch_k * 2, pitch_k, pitch_v, dkt, dvt,
+                               lane, b0, w_all_valid && b0 + kMmKeys <= w_nb_all, blo_r, bhi_r, a.scale * kLog2e,
+                               a.weights, bias_r, m_run, l_run, o);
+      __syncthreads();
+      continue;
+    }
+    const int j0 = k_lo + (t - nbt) * kMmKeys;
     // a warp whose rows see nothing of this tile skips it (uniform per warp)
     const int w_hi = min(start + tok0 + min((warp * 16 + 15) / g, n_tok - 1), pos_last);
     const int w_first_tok = (warp * 16) / g;
@@ -338,7 +393,7 @@ attention_masked_prefill_kernel(const MaskedArgs a) {
     float l = l_run[h];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
-    const float inv = a.weights == 2 ? 1.f : (l > 0.f ? 1.f / l : 0.f);
+    const float inv = a.weights == 2 ? a.out_scale : (l > 0.f ? a.out_scale / l : 0.f);
     const int r = warp * 16 + gq + 8 * h;
     const int tl = r / g, hg = r - tl * g;
     if (tl >= n_tok) continue;
@@ -384,16 +439,19 @@ attention_masked_decode_kernel(const MaskedArgs a) {
     __syncthreads();
   }
   const int k_lo = mm_first_seen(a.mask, a.mask_size, pos);
-  const int n_tiles = (pos - k_lo) / kDecKeys + 1;
+  const int nb = mm_blocks_seen(a.mask, a.mask_size, a.pool, pos);     // tiles of block rows come first
+  const int nbt = (nb + kDecKeys - 1) / kDecKeys;
+  const int n_tiles = nbt + (pos - k_lo) / kDecKeys + 1;
   const int per_split = (n_tiles + a.splits - 1) / a.splits;
   const int t_begin = split * per_split, t_end = min(n_tiles, t_begin + per_split);
   const int gq = lane >> 2;
-  int lo_r[2], hi_r[2];
+  int lo_r[2], hi_r[2], blo_r[2] = {0, 0}, bhi_r[2];
   float bias_r[2];
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const int r = gq + 8 * h;
     hi_r[h] = r < g ? pos : -1;
+    bhi_r[h] = r < g ? nb - 1 : -1;
     lo_r[h] = k_lo;
     bias_r[h] = (a.weights == 2 && r < g) ? a.bias[kvh * g + r] * kLog2e : 0.f;
   }
@@ -402,13 +460,15 @@ attention_masked_decode_kernel(const MaskedArgs a) {
 #pragma unroll
   for (int n = 0; n < 2 * DVT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
   for (int t = t_begin + warp; t < t_end; t += 4) {
-    const int j0 = k_lo + t * kDecKeys;
-    load_kv_tile_warp(a, seq, kvh, j0, k_lo, pos, my_k, my_v, pitch_k, pitch_v, lane, row, kDecKeys, slot_s[warp]);
+    const bool blocks = t < nbt;
+    const int j0 = blocks ? t * kDecKeys : k_lo + (t - nbt) * kDecKeys;
+    load_kv_tile_warp(a, seq, kvh, j0, blocks ? 0 : k_lo, blocks ? nb - 1 : pos, my_k, my_v, pitch_k, pitch_v, lane, row,
+                      kDecKeys, slot_s[warp], blocks);
     asm volatile("cp.async.commit_group;" ::: "memory");
     asm volatile("cp.async.wait_group 0;" ::: "memory");
     __syncwarp();
-    tile_step<DKT, DVT, kDecKeys / 8>(q_s, my_k, my_v, pitch_k, pitch_v, dkt, dvt, lane, j0, false, lo_r, hi_r, a.scale * kLog2e,
-                        a.weights, bias_r, m_run, l_run, o);
+    tile_step<DKT, DVT, kDecKeys / 8>(q_s, my_k, my_v, pitch_k, pitch_v, dkt, dvt, lane, j0, false, blocks ? blo_r : lo_r,
+                                      blocks ? bhi_r : hi_r, a.scale * kLog2e, a.weights, bias_r, m_run, l_run, o);
     __syncwarp();
   }
   // the four warps' partial results into shared memory (over the tiles, which are done with)
@@ -449,7 +509,7 @@ attention_masked_decode_kernel(const MaskedArgs a) {
     }
     if (a.weights == 1 && last) l += fast_exp2(-m);
     if (last) {
-      const float inv = a.weights == 2 ? 1.f : (l > 0.f ? 1.f / l : 0.f);
+      const float inv = a.weights == 2 ? a.out_scale : (l > 0.f ? a.out_scale / l : 0.f);
       __nv_bfloat16* dst = a.out + (size_t)row * a.out_stride + (size_t)(kvh * g + r) * a.dv;
       for (int c = lane; c < a.dv; c += 32) {
         float v = 0.f;
@@ -489,7 +549,7 @@ attention_masked_merge_kernel(const MaskedArgs a) {
     const float ms = src[s * step + a.dv];
     if (a.weights != 2 && ms != -INFINITY) l += fast_exp2(ms - m) * src[s * step + a.dv + 1];
   }
-  const float inv = a.weights == 2 ? 1.f : (l > 0.f ? 1.f / l : 0.f);
+  const float inv = a.weights == 2 ? a.out_scale : (l > 0.f ? a.out_scale / l : 0.f);
   __nv_bfloat16* dst = a.out + (size_t)a.q_start[seq] * a.out_stride + (size_t)h * a.dv;
   for (int c = threadIdx.x; c < a.dv; c += blockDim.x) {
     float v = 0.f;
@@ -566,6 +626,45 @@ extern "C" int leone_attention_masked_mma(const void* qkv, int row_stride, void*
   MaskedArgs a{(const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
                (const __nv_bfloat16*)v_pool, block_table, table_width, q_start, ctx_len, n_q, n_kv, dk, dv, scale, mask,
                mask_size, weights, bias, page_tokens, num_pages, splits, partial, status};
+  const bool wide_k = dk > 64, wide_v = dv > 64;
+  if (wide_k && wide_v) return launch_masked<8, 8>(a, n_seqs, max_q_len, decode != 0, stream);
+  if (wide_k) return launch_masked<8, 4>(a, n_seqs, max_q_len, decode != 0, stream);
+  if (wide_v) return launch_masked<4, 8>(a, n_seqs, max_q_len, decode != 0, stream);
+  return launch_masked<4, 4>(a, n_seqs, max_q_len, decode != 0, stream);
+}
+
+// The same with mask 3, a window of `window` token rows and before it the rows of the cache of block
+// means (pool positions a row); `q` holds the query heads only, the output rows are multiplied by
+// out_scale.  Softmax weights.
+extern "C" int leone_attention_pooled_mma(const void* q, int ldq, void* out, int out_stride, const void* k_pool,
+                                          const void* v_pool, const int* block_table, int table_width, int num_pages,
+                                          int page_tokens, const void* kb_pool, const void* vb_pool,
+                                          const int* pool_table, int pool_table_width, int pool_pages, int pool_rows,
+                                          const int* q_start, const int* ctx_len, int n_seqs, int max_q_len, int n_q,
+                                          int n_kv, int dk, int dv, float scale, int window, int pool, float out_scale,
+                                          int decode, int splits, float* partial, int* status, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  if (!leone_attention_masked_mma_supported(n_q, n_kv, dk, dv, decode)) return kRefusedSize;
+  if (window <= 0 || pool <= 0 || kb_pool == nullptr || vb_pool == nullptr || pool_table == nullptr ||
+      pool_table_width <= 0 || pool_rows < (page_tokens + pool - 1) / pool)
+    return kRefusedSize;
+  if (ldq % 8 != 0 || out_stride % 2 != 0 || ((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15) ||
+      ((uintptr_t)kb_pool & 15) || ((uintptr_t)vb_pool & 15) || ((uintptr_t)out & 3))
+    return kRefusedAlignment;
+  if (n_kv > 65535 || n_seqs > 65535 || page_tokens <= 0 || table_width <= 0) return kRefusedSize;
+  if (!decode) splits = 1;
+  if (splits < 1 || splits > 64 || (splits > 1 && partial == nullptr)) return kRefusedSize;
+  MaskedArgs a{(const __nv_bfloat16*)q, ldq, (__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)k_pool,
+               (const __nv_bfloat16*)v_pool, block_table, table_width, q_start, ctx_len, n_q, n_kv, dk, dv, scale, 3,
+               window, 0, nullptr, page_tokens, num_pages, splits, partial, status};
+  a.kb_pool = (const __nv_bfloat16*)kb_pool;
+  a.vb_pool = (const __nv_bfloat16*)vb_pool;
+  a.pool_table = pool_table;
+  a.pool_table_width = pool_table_width;
+  a.pool_pages = pool_pages;
+  a.pool_rows = pool_rows;
+  a.pool = pool;
+  a.out_scale = out_scale;
   const bool wide_k = dk > 64, wide_v = dv > 64;
   if (wide_k && wide_v) return launch_masked<8, 8>(a, n_seqs, max_q_len, decode != 0, stream);
   if (wide_k) return launch_masked<8, 4>(a, n_seqs, max_q_len, decode != 0, stream);

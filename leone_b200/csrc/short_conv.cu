@@ -38,8 +38,8 @@ short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w
     if (threadIdx.x == 0) set_status(status, kBadSequence, t, s);
     return;
   }
-  const int slot = slot_ids[s];
-  if (slot < 0 || slot >= n_slots) {
+  const int slot = taps > 1 ? slot_ids[s] : 0;      // one tap: no state, no slot
+  if (slot < 0 || (taps > 1 && slot >= n_slots)) {
     if (threadIdx.x == 0) set_status(status, kBadSequence, t, slot);
     return;
   }

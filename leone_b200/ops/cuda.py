@@ -792,13 +792,41 @@ class CudaOps:
               and out.dtype == q.dtype == tokens.k_pool.dtype, "attention_pooled layout")
         args = self._pooled_args(tokens, blocks, n_kv, dk, dv, pool)
         self.launches += 1
-        if self.fast is not None and hasattr(self.fast, "attention_pooled") and \
-                self.fast.attention_pooled(self, ctx, q, out, args, n_q, n_kv, dk, dv, scale, window, pool, out_scale):
+        if self.fast is not None and self.attention_pooled_tiled(ctx, q, out, args, n_q, n_kv, dk, dv, scale, window,
+                                                                 pool, out_scale):
             return
         _check(self.mixers.leone_attention_pooled(
             _dt(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), *args, _ptr(ctx.seq_of_token),
             _ptr(ctx.positions), n, n_q, n_kv, dk, dv, c_float(scale), int(window), int(pool), c_float(out_scale),
             ctx.n_seqs, _ptr(ctx.status), self._stream()), "attention_pooled")
+
+    def attention_pooled_tiled(self, ctx, q, out, args, n_q, n_kv, dk, dv, scale, window, pool, out_scale) -> bool:
+        """The tensor-core form of :meth:`attention_pooled`: the masked attention of
+        ``csrc/attention_masked_mma.cu`` with its mask of a window and pooled blocks before it, for
+        the sizes that kernel takes (bfloat16, key and value widths multiples of 16 up to 128).  A
+        decode step's members (block rows, then token rows) are split over blocks until the SMs are busy."""
+        decode = bool(ctx.decode_only)
+        if (q.dtype != torch.bfloat16 or os.environ.get("LEONE_NO_POOLED_MMA", "0") == "1"
+                or getattr(ctx, "q_start", None) is None
+                or not self.mixers.leone_attention_masked_mma_supported(n_q, n_kv, dk, dv, 1 if decode else 0)
+                or q.stride(0) % 8 or out.stride(0) % 2):
+            return False
+        splits, partial = 1, None
+        if decode:
+            longest = int(ctx.max_ctx_len)
+            tiles = -(-min(int(window), longest) // 32) + 1 + -(-(max(longest - int(window), 0) // int(pool)) // 32)
+            splits = max(1, min(64, tiles // 8, (3 * 148) // max(ctx.n_seqs * n_kv, 1)))
+            if splits > 1:
+                self.mixers.leone_attention_masked_mma_scratch.restype = ctypes.c_longlong
+                need = int(self.mixers.leone_attention_masked_mma_scratch(ctx.n_seqs, n_kv, dv, splits))
+                partial = self._scratch("masked_partial", -(-need // 64), 64, torch.float32)
+                self.launches += 1
+        _check(self.mixers.leone_attention_pooled_mma(
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), *args, _ptr(ctx.q_start), _ptr(ctx.ctx_len), ctx.n_seqs,
+            1 if decode else int(ctx.max_q_len), n_q, n_kv, dk, dv, c_float(scale), int(window), int(pool),
+            c_float(out_scale), 1 if decode else 0, splits, _ptr(partial), _ptr(ctx.status), self._stream()),
+            "attention_pooled_mma")
+        return True
 
     def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
         """``hidden += sum over each token's chosen experts``; scratch comes from ``rt``.

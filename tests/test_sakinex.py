@@ -227,6 +227,22 @@ def test_each_layer_alone(which, index):
 
 
 @pytest.mark.gpu
+def test_convolutions_of_one_tap():
+    """One tap in every convolution (in front of the sublayers and on q, k, v): nothing is carried from
+    token to token, and no state is asked for; two taps beside it."""
+    for canon, conv in ((1, 1), (1, 2), (2, 1)):
+        raw = model(80, 48, 1e-6, 0.7, canon=canon, layers=[
+            layer(mixer(left(4, 2, 8, 12, 0.3, 6, 3, conv=conv, rot_dims=4), 24, 1.0, 0.8), moe(16, 4, 2, shared=8)),
+            layer(mixer(left(2, 2, 16, 8, 0.2, 11, 2, conv=conv), 40, 0.9, 1.0), None)])
+        tensors = _random(raw, 21 + canon + conv)
+        reqs = _requests(80, [37, 5, 18], seed=3)
+        steps = replay.trace_mixed(reqs, seed=4)
+        eng = _engine(None, tensors, "float32", "cuda:0", max_tokens=replay.max_live_tokens(steps), page=8, raw=raw)
+        out = replay.run_trace_engine(eng, steps)
+        replay.compare(steps, out, plain.PlainSakinex(raw, tensors), reqs, what=f"taps {canon}, {conv}", **FP32)
+
+
+@pytest.mark.gpu
 def test_long_prompt_and_long_decode():
     """A prompt of many pages, then 150 single-token steps across pages, windows and blocks;
     position 0 alone first.  The prompt is long enough for the recurrence to run in chunks."""
