@@ -20,7 +20,8 @@
 // and k head divided by its root mean square (eps inside the root); q to q_out, k and v into their pages.
 //
 // leone_attention_pool_blocks (a block per (token, kv head)): a token whose position ends a block writes
-// the block's mean key and value (fp32 sums in ascending position over the rows as the cache holds them).
+// the block's mean key and value (fp32 sums over the rows as the cache holds them: every eighth row in
+// ascending position by each of eight warps, then the eight sums in order).
 //
 // leone_attention_pooled: a block per (token, head); scores and weights fp32, online over tiles of 128
 // members (blocks first, then tokens, ascending).  A row depends on its own sequence only.
@@ -134,8 +135,12 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
   }
 }
 
+constexpr int kBlockMeanThreads = 256, kBlockMeanWarps = kBlockMeanThreads / 32, kBlockMeanSlab = 512;
+
+// The eight warps of a block take every eighth row of the pooled block each, lanes over columns (in
+// slabs of kBlockMeanSlab); the warps' sums meet in shared memory in ascending order.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kBlockMeanThreads)
 attention_pool_blocks_kernel(const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                              const int* __restrict__ block_table, int table_width, int num_pages, int page_tokens,
                              T* __restrict__ kb_pool, T* __restrict__ vb_pool, const int* __restrict__ pool_table,
@@ -144,7 +149,9 @@ attention_pool_blocks_kernel(const T* __restrict__ k_pool, const T* __restrict__
                              int* status) {
   pdl_trigger();
   pdl_wait();
-  const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x;
+  __shared__ float part[kBlockMeanWarps][kBlockMeanSlab];
+  __shared__ int bad;
+  const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int pos = positions[t], s = seq_of_token[t];
   if (pos < 0 || s < 0 || s >= n_seqs) return;               // the preparation reported it
   if ((pos + 1) % pool != 0) return;                         // this token ends no block
@@ -154,24 +161,47 @@ attention_pool_blocks_kernel(const T* __restrict__ k_pool, const T* __restrict__
     if (tid == 0) set_status(status, kBadPage, t, dst_page, pos);
     return;
   }
+  if (tid == 0) bad = 0;
+  __syncthreads();
   const long long dst = ((long long)dst_page * n_kv + g) * pool_rows + (pos % page_tokens) / pool;
-  for (int c = tid; c < dk + dv; c += 128) {
-    const bool key = c < dk;
-    const int e = key ? c : c - dk, width = key ? dk : dv;
-    const T* src = key ? k_pool : v_pool;
-    float sum = 0.f;
-    bool ok = true;
-    for (int j = pos - pool + 1; j <= pos; ++j) {
+  const int first = pos - pool + 1, width = dk + dv;
+  for (int c0 = 0; c0 < width; c0 += kBlockMeanSlab) {
+    const int cn = min(kBlockMeanSlab, width - c0);
+    float sum[kBlockMeanSlab / 32];
+#pragma unroll
+    for (int i = 0; i < kBlockMeanSlab / 32; ++i) sum[i] = 0.f;
+    for (int j = first + warp; j <= pos; j += kBlockMeanWarps) {
       const int b = j / page_tokens;
       const int page = b < table_width ? block_table[(size_t)s * table_width + b] : -1;
       if (page < 0 || page >= num_pages) {
-        set_status(status, kBadPage, t, page, j);
-        ok = false;
-        break;
+        if (lane == 0) {
+          set_status(status, kBadPage, t, page, j);
+          bad = 1;
+        }
+        continue;
       }
-      sum += to_float<T>(src[(((long long)page * n_kv + g) * page_tokens + (j % page_tokens)) * width + e]);
+      const long long at = ((long long)page * n_kv + g) * page_tokens + (j % page_tokens);
+#pragma unroll
+      for (int i = 0; i < kBlockMeanSlab / 32; ++i) {
+        const int c = c0 + lane + 32 * i;
+        if (lane + 32 * i < cn) sum[i] += c < dk ? to_float<T>(k_pool[at * dk + c]) : to_float<T>(v_pool[at * dv + (c - dk)]);
+      }
     }
-    if (ok) (key ? kb_pool : vb_pool)[dst * width + e] = from_float<T>(sum / (float)pool);
+#pragma unroll
+    for (int i = 0; i < kBlockMeanSlab / 32; ++i)
+      if (lane + 32 * i < cn) part[warp][lane + 32 * i] = sum[i];
+    __syncthreads();
+    if (!bad) {
+      for (int cc = tid; cc < cn; cc += kBlockMeanThreads) {
+        float total = 0.f;
+#pragma unroll
+        for (int w = 0; w < kBlockMeanWarps; ++w) total += part[w][cc];
+        const int c = c0 + cc;
+        if (c < dk) kb_pool[dst * dk + c] = from_float<T>(total / (float)pool);
+        else vb_pool[dst * dv + (c - dk)] = from_float<T>(total / (float)pool);
+      }
+    }
+    __syncthreads();
   }
 }
 
@@ -344,7 +374,7 @@ extern "C" int leone_attention_pool_blocks(int dtype, const void* k_pool, const 
     return kRefusedSize;
   const dim3 grid(n_tokens, n_kv);
 #define LAUNCH(T)                                                                                                    \
-  return launch_kernel(attention_pool_blocks_kernel<T>, grid, dim3(128), 0, stream, (const T*)k_pool, (const T*)v_pool, \
+  return launch_kernel(attention_pool_blocks_kernel<T>, grid, dim3(kBlockMeanThreads), 0, stream, (const T*)k_pool, (const T*)v_pool, \
                        block_table, table_width, num_pages, page_tokens, (T*)kb_pool, (T*)vb_pool, pool_table,       \
                        pool_table_width, pool_pages, pool_rows, positions, seq_of_token, n_seqs, n_kv, dk, dv, pool,  \
                        status)

@@ -57,6 +57,93 @@ short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w
   out[(size_t)t * ldo + c] = from_float<TO>(acc);
 }
 
+// The same for kConvTile consecutive tokens of a channel per thread (steps of many tokens): where the
+// tile's tokens belong to one sequence, the kConvTile + taps - 1 inputs they read are loaded once and
+// every output is formed from registers; a tile that spans sequences falls back to token-by-token.
+constexpr int kConvTile = 8;
+
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(kConvThreads)
+short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ state,
+                       TO* __restrict__ out, int ldo, const int* __restrict__ q_start,
+                       const int* __restrict__ seq_of_token, const int* __restrict__ slot_ids, int n_tokens, int channels,
+                       int taps, int add_input, int n_seqs, int n_slots, int* status) {
+  pdl_trigger();
+  pdl_wait();
+  const int t0 = blockIdx.x * kConvTile, c = blockIdx.y * kConvThreads + threadIdx.x;
+  if (c >= channels) return;
+  const int t_end = min(t0 + kConvTile, n_tokens);
+  const int s0 = seq_of_token[t0], s1 = seq_of_token[t_end - 1];
+  if (s0 == s1 && s0 >= 0 && s0 < n_seqs) {
+    const int slot = taps > 1 ? slot_ids[s0] : 0;
+    if (slot < 0 || (taps > 1 && slot >= n_slots)) {
+      if (threadIdx.x == 0) set_status(status, kBadSequence, t0, slot);
+      return;
+    }
+    const int local0 = t0 - q_start[s0];
+    const float* st = state + (size_t)slot * (taps - 1) * channels;
+    float v[kConvTile + kMaxTaps - 1];
+    // input r of the tile is the sequence's token local0 - (taps - 1) + r of this step, or a state row before it
+#pragma unroll
+    for (int r = 0; r < kConvTile + kMaxTaps - 1; ++r) {
+      v[r] = 0.f;
+      if (r < kConvTile + taps - 1) {
+        const int i = local0 - (taps - 1) + r;
+        if (i >= 0) {
+          if (t0 - (taps - 1) + r < t_end) v[r] = to_float<TI>(x[(size_t)(t0 - (taps - 1) + r) * ldx + c]);
+        } else {
+          v[r] = st[(size_t)(taps - 1 + i) * channels + c];
+        }
+      }
+    }
+    float wt[kMaxTaps];
+#pragma unroll
+    for (int j = 0; j < kMaxTaps; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
+#pragma unroll
+    for (int i = 0; i < kConvTile; ++i) {
+      if (t0 + i < t_end) {
+        float acc = 0.f;
+#pragma unroll
+        for (int j = 0; j < kMaxTaps; ++j)
+          if (j < taps) acc = fmaf(wt[j], v[i + j], acc);
+        // the token's own input is v[i + taps - 1]: picked by a static index
+        if (add_input) {
+          float own = 0.f;
+#pragma unroll
+          for (int j = 0; j < kMaxTaps; ++j)
+            if (j == taps - 1) own = v[i + j];
+          acc += own;
+        }
+        out[(size_t)(t0 + i) * ldo + c] = from_float<TO>(acc);
+      }
+    }
+    return;
+  }
+  for (int t = t0; t < t_end; ++t) {
+    const int s = seq_of_token[t];
+    if (s < 0 || s >= n_seqs) {
+      if (threadIdx.x == 0) set_status(status, kBadSequence, t, s);
+      continue;
+    }
+    const int slot = taps > 1 ? slot_ids[s] : 0;
+    if (slot < 0 || (taps > 1 && slot >= n_slots)) {
+      if (threadIdx.x == 0) set_status(status, kBadSequence, t, slot);
+      continue;
+    }
+    const int local = t - q_start[s];
+    const float* st = state + (size_t)slot * (taps - 1) * channels;
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {
+      const int back = taps - 1 - j;
+      const float u = back <= local ? to_float<TI>(x[(size_t)(t - back) * ldx + c])
+                                    : st[(size_t)(taps - 1 + local - back) * channels + c];
+      acc = fmaf(w[(size_t)c * taps + j], u, acc);
+    }
+    if (add_input) acc += to_float<TI>(x[(size_t)t * ldx + c]);
+    out[(size_t)t * ldo + c] = from_float<TO>(acc);
+  }
+}
+
 template <typename TI>
 __global__ void __launch_bounds__(kConvThreads)
 short_conv_state_kernel(const TI* __restrict__ x, int ldx, float* __restrict__ state, const int* __restrict__ q_start,
@@ -87,6 +174,41 @@ short_conv_state_kernel(const TI* __restrict__ x, int ldx, float* __restrict__ s
 
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 
+// Tokens first .. last - 1 of one channel.  The loads of kGruAhead tokens are issued before their
+// arithmetic, so that a thread has that many rows in flight instead of one; the arithmetic per token
+// and its order are the same however the tokens are grouped.
+constexpr int kGruAhead = 8;
+
+template <typename TP, typename TO, bool kOut, bool kProduct>
+__device__ __forceinline__ void min_gru_walk(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g_off,
+                                             float bz, float bx, int c, int first, int last, float& S, float& A,
+                                             TO* __restrict__ out, int ldo, float out_scale) {
+  for (int t0 = first; t0 < last; t0 += kGruAhead) {
+    float pz[kGruAhead], px[kGruAhead], pg[kGruAhead];
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i) {
+      const TP* row = proj + (size_t)min(t0 + i, last - 1) * ldp;
+      pz[i] = to_float<TP>(row[z_off + c]);
+      px[i] = to_float<TP>(row[x_off + c]);
+      if (kOut) pg[i] = to_float<TP>(row[g_off + c]);
+    }
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i) {
+      if (t0 + i < last) {
+        const float z = sigmoid_f(pz[i] + bz);
+        const float u = px[i] + bx;
+        const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+        S = (1.f - z) * S + z * cand;
+        if (kProduct) A *= 1.f - z;
+        if (kOut) {
+          const float g = pg[i];
+          out[(size_t)(t0 + i) * ldo + c] = from_float<TO>(out_scale * S * (g * sigmoid_f(g)));
+        }
+      }
+    }
+  }
+}
+
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kConvThreads)
 min_gru_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g_off, const float* __restrict__ z_b,
@@ -104,16 +226,8 @@ min_gru_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g
   }
   const int first = q_start[s], last = q_start[s + 1];
   const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
-  float S = state[(size_t)slot * width + c];
-  for (int t = first; t < last; ++t) {
-    const TP* row = proj + (size_t)t * ldp;
-    const float z = sigmoid_f(to_float<TP>(row[z_off + c]) + bz);
-    const float u = to_float<TP>(row[x_off + c]) + bx;
-    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-    S = (1.f - z) * S + z * cand;
-    const float g = to_float<TP>(row[g_off + c]);
-    out[(size_t)t * ldo + c] = from_float<TO>(out_scale * S * (g * sigmoid_f(g)));
-  }
+  float S = state[(size_t)slot * width + c], A = 1.f;
+  min_gru_walk<TP, TO, true, false>(proj, ldp, z_off, x_off, g_off, bz, bx, c, first, last, S, A, out, ldo, out_scale);
   state[(size_t)slot * width + c] = S;
 }
 
@@ -133,14 +247,8 @@ min_gru_chunk_sums_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x
   if (c >= width) return;
   const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
   float A = 1.f, S = 0.f;
-  for (int t = chunk_first[k]; t < chunk_last[k]; ++t) {
-    const TP* row = proj + (size_t)t * ldp;
-    const float z = sigmoid_f(to_float<TP>(row[z_off + c]) + bz);
-    const float u = to_float<TP>(row[x_off + c]) + bx;
-    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-    S = (1.f - z) * S + z * cand;
-    A *= 1.f - z;
-  }
+  min_gru_walk<TP, float, false, true>(proj, ldp, z_off, x_off, 0, bz, bx, c, chunk_first[k], chunk_last[k], S, A,
+                                       nullptr, 0, 0.f);
   chunk_a[(size_t)k * width + c] = A;
   chunk_s[(size_t)k * width + c] = S;
 }
@@ -159,10 +267,22 @@ min_gru_chunk_prefix_kernel(const int* __restrict__ seq_chunk_start, const int* 
     return;
   }
   float S = state[(size_t)slot * width + c];
-  for (int k = seq_chunk_start[s]; k < seq_chunk_start[s + 1]; ++k) {
-    const float end = chunk_a[(size_t)k * width + c] * S + chunk_s[(size_t)k * width + c];
-    chunk_s[(size_t)k * width + c] = S;            // from here on: the state at the chunk's start
-    S = end;
+  const int k_first = seq_chunk_start[s], k_last = seq_chunk_start[s + 1];
+  for (int k0 = k_first; k0 < k_last; k0 += kGruAhead) {
+    float a[kGruAhead], b[kGruAhead];
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i) {
+      const int k = min(k0 + i, k_last - 1);
+      a[i] = chunk_a[(size_t)k * width + c];
+      b[i] = chunk_s[(size_t)k * width + c];
+    }
+#pragma unroll
+    for (int i = 0; i < kGruAhead; ++i) {
+      if (k0 + i < k_last) {
+        chunk_s[(size_t)(k0 + i) * width + c] = S;       // from here on: the state at the chunk's start
+        S = a[i] * S + b[i];
+      }
+    }
   }
   state[(size_t)slot * width + c] = S;
 }
@@ -178,16 +298,9 @@ min_gru_chunk_out_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_
   const int k = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
   if (c >= width) return;
   const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
-  float S = chunk_s[(size_t)k * width + c];
-  for (int t = chunk_first[k]; t < chunk_last[k]; ++t) {
-    const TP* row = proj + (size_t)t * ldp;
-    const float z = sigmoid_f(to_float<TP>(row[z_off + c]) + bz);
-    const float u = to_float<TP>(row[x_off + c]) + bx;
-    const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
-    S = (1.f - z) * S + z * cand;
-    const float g = to_float<TP>(row[g_off + c]);
-    out[(size_t)t * ldo + c] = from_float<TO>(out_scale * S * (g * sigmoid_f(g)));
-  }
+  float S = chunk_s[(size_t)k * width + c], A = 1.f;
+  min_gru_walk<TP, TO, true, false>(proj, ldp, z_off, x_off, g_off, bz, bx, c, chunk_first[k], chunk_last[k], S, A, out,
+                                    ldo, out_scale);
 }
 
 template <typename T>
@@ -229,9 +342,18 @@ extern "C" int leone_short_conv(int in_dtype, int out_dtype, const void* x, int 
   if (channels <= 0 || taps < 1 || taps > kMaxTaps || ldx < channels || ldo < channels) return kRefusedSize;
   if (taps > 1 && state == nullptr) return kRefusedSize;
   const dim3 grid(n_tokens, (channels + kConvThreads - 1) / kConvThreads);
-#define LAUNCH(TI, TO)                                                                                            \
-  return launch_kernel(short_conv_kernel<TI, TO>, grid, dim3(kConvThreads), 0, stream, (const TI*)x, ldx, w, state, \
-                       (TO*)out, ldo, q_start, seq_of_token, slot_ids, channels, taps, add_input, n_seqs, n_slots, status)
+  const bool tiled = n_tokens >= 16 * kConvTile;        // a decode step's tokens each belong to another sequence
+  const dim3 tile_grid((n_tokens + kConvTile - 1) / kConvTile, grid.y);
+#define LAUNCH(TI, TO)                                                                                              \
+  {                                                                                                                 \
+    if (tiled)                                                                                                      \
+      return launch_kernel(short_conv_tile_kernel<TI, TO>, tile_grid, dim3(kConvThreads), 0, stream, (const TI*)x,  \
+                           ldx, w, state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, n_tokens, channels, taps, \
+                           add_input, n_seqs, n_slots, status);                                                     \
+    return launch_kernel(short_conv_kernel<TI, TO>, grid, dim3(kConvThreads), 0, stream, (const TI*)x, ldx, w,      \
+                         state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, channels, taps, add_input, n_seqs,  \
+                         n_slots, status);                                                                          \
+  }
   if (in_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
   if (in_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);
   if (in_dtype == 1 && out_dtype == 1) LAUNCH(__nv_bfloat16, __nv_bfloat16);

@@ -250,6 +250,110 @@ def bench_masked_attention(ops, tokens, batch, context, n_q, n_kv, dk, dv, mask,
     return row
 
 
+def _step_of(seqs: int, q_len: int, ctx_len: int):
+    """What the kernels read of a step: ``seqs`` sequences that each bring ``q_len`` tokens ending at ``ctx_len``."""
+    n = seqs * q_len
+    return types.SimpleNamespace(
+        q_start=torch.arange(seqs + 1, device=DEV, dtype=torch.int32) * q_len,
+        ctx_len=torch.full((seqs,), ctx_len, device=DEV, dtype=torch.int32),
+        positions=(torch.arange(q_len, device=DEV, dtype=torch.int32) + (ctx_len - q_len)).repeat(seqs),
+        seq_of_token=torch.arange(seqs, device=DEV, dtype=torch.int32).repeat_interleave(q_len),
+        slot_ids=torch.arange(seqs, device=DEV, dtype=torch.int32),
+        status=torch.zeros(4, device=DEV, dtype=torch.int32), n_seqs=seqs, n_tokens=n, max_q_len=q_len,
+        max_ctx_len=ctx_len, decode_only=q_len == 1, q_lens=[q_len] * seqs)
+
+
+def bench_pooled_attention(ops, tokens, batch, context, n_q, n_kv, dk, dv, window, pool, page_tokens, reps, warmup,
+                           taps=4):
+    """Attention over a window and pooled blocks before it (``CudaOps.attention_pooled``), the step's
+    preparation (convolution, rotation, unit norm, cache write: ``attention_pooled_prepare``) and the
+    block means (``attention_pool_blocks``): one prompt of ``tokens`` tokens, or with ``batch`` a decode
+    step of that many sequences at ``context`` keys."""
+    decode = batch > 0
+    seqs, length = (batch, context) if decode else (1, tokens)
+    pages = -(-length // page_tokens)
+    rows_per_page = -(-page_tokens // pool)
+    bf = torch.bfloat16
+    table = torch.randperm(seqs * pages, device=DEV).to(torch.int32).view(seqs, pages)
+    tok = types.SimpleNamespace(k_pool=torch.randn((seqs * pages, n_kv, page_tokens, dk), device=DEV).to(bf),
+                                v_pool=torch.randn((seqs * pages, n_kv, page_tokens, dv), device=DEV).to(bf),
+                                block_table=table, page_tokens=page_tokens, writes=True)
+    blk = types.SimpleNamespace(k_pool=torch.randn((seqs * pages, n_kv, rows_per_page, dk), device=DEV).to(bf),
+                                v_pool=torch.randn((seqs * pages, n_kv, rows_per_page, dv), device=DEV).to(bf),
+                                block_table=table, page_tokens=page_tokens, tokens_per_row=pool, writes=True)
+    q_len = 1 if decode else tokens
+    ctx = _step_of(seqs, q_len, length)
+    n = seqs * q_len
+    cols = (n_q + n_kv) * dk + n_kv * dv
+    proj = torch.randn((n, cols), device=DEV)
+    q = torch.randn((n, n_q * dk), device=DEV).to(bf)
+    out = torch.empty((n, n_q * dv), device=DEV, dtype=bf)
+    conv_w = torch.randn((cols, taps), device=DEV) if taps else None
+    state = torch.zeros((seqs, taps - 1, cols), device=DEV) if taps > 1 else None
+    freqs = torch.rand(dk // 2, device=DEV)
+    result = []
+
+    def seen(p):
+        return min(p + 1, window) + max(p - window + 1, 0) // pool
+    members = seqs * seen(length - 1) if decode else sum(seen(p) for p in range(tokens))
+    ms = _time(lambda: ops.attention_pooled(ctx, q, out, tok, blk, n_q, n_kv, dk, dv, dk ** -0.5, window, pool), reps, warmup)
+    row = dict(kernel="attention_pooled", window=window, pool=pool, dk=dk, dv=dv, us=ms * 1e3)
+    if decode:
+        row.update(batch=batch, context=context, gbs=members * n_kv * (dk + dv) * 2.0 / ms / 1e6)
+    else:
+        row.update(tokens=tokens, tflops=2.0 * n_q * (dk + dv) * members / ms / 1e9)
+    result.append(row)
+    ms = _time(lambda: ops.attention_pooled_prepare(ctx, proj, q, n_q, n_kv, dk, dv, conv_w, state, freqs, "half_split",
+                                                    1.0, True, 1e-6, tok), reps, warmup)
+    moved = n * (cols * 4 * (2 if decode and taps > 1 else 1) + cols * 2)        # rows read (state rows too in a decode step), q and pages written
+    result.append(dict(kernel="attention_pooled_prepare", tokens=n, cols=cols, taps=taps, us=ms * 1e3, gbs=moved / ms / 1e6))
+    ms = _time(lambda: ops.attention_pool_blocks(ctx, tok, blk, n_kv, dk, dv, pool), reps, warmup)
+    ended = seqs * (1 if decode and length % pool == 0 else 0) if decode else tokens // pool
+    moved = ended * n_kv * (dk + dv) * 2 * (pool + 1)
+    result.append(dict(kernel="attention_pool_blocks", tokens=n, blocks=ended, us=ms * 1e3, gbs=moved / ms / 1e6))
+    return result
+
+
+def bench_conv_and_gru(ops, tokens, batch, width, taps, chunk, reps, warmup):
+    """The short convolution with state in front of a sublayer (fp32 rows in, bfloat16 rows out), its
+    state update, and the minGRU recurrence over fp32 projections ``[z | x | g]``: one prompt of
+    ``tokens`` tokens, or with ``batch`` a decode step of that many sequences."""
+    decode = batch > 0
+    seqs, q_len = (batch, 1) if decode else (1, tokens)
+    ctx = _step_of(seqs, q_len, 4096)
+    n = seqs * q_len
+    copies = max(1, min(16, (160 << 20) // max(n * width * 16, 1)))     # together larger than L2
+    xs = [torch.randn((n, width), device=DEV) for _ in range(copies)]
+    outs = [torch.empty((n, width), device=DEV, dtype=torch.bfloat16) for _ in range(copies)]
+    projs = [torch.randn((n, 3 * width), device=DEV) for _ in range(copies)]
+    w = torch.randn((width, taps), device=DEV)
+    state = torch.zeros((seqs, taps - 1, width), device=DEV)
+    gru_state = torch.zeros((seqs, width), device=DEV)
+    bias = torch.zeros(width, device=DEV)
+    turn = [0]
+
+    def rotate(fn):
+        def run():
+            i = turn[0] = (turn[0] + 1) % copies
+            fn(i)
+        return run
+    result = []
+    ms = _time(rotate(lambda i: ops.short_conv(ctx, xs[i], w, state, outs[i], add_input=True)), reps, warmup, per_graph=copies)
+    result.append(dict(kernel="short_conv", tokens=n, width=width, taps=taps, us=ms * 1e3, gbs=n * width * 6.0 / ms / 1e6))
+    ms = _time(rotate(lambda i: ops.short_conv_state(ctx, xs[i], state)), reps, warmup, per_graph=copies)
+    moved = seqs * (taps - 1) * width * (12 if decode else 8)
+    result.append(dict(kernel="short_conv_state", tokens=n, width=width, taps=taps, us=ms * 1e3, gbs=moved / ms / 1e6))
+    use_chunk = chunk if (not decode and tokens > 2 * chunk) else 0
+    ms = _time(rotate(lambda i: ops.min_gru(ctx, projs[i], bias, bias, gru_state, outs[i], chunk=use_chunk)), reps, warmup,
+               per_graph=copies)
+    result.append(dict(kernel="min_gru", tokens=n, width=width, chunk=use_chunk, us=ms * 1e3,
+                       gbs=n * width * 14.0 / ms / 1e6))
+    norm_w = torch.ones(width, device=DEV, dtype=torch.bfloat16)
+    ms = _time(rotate(lambda i: ops.rms_norm(xs[i], norm_w, outs[i], 1e-6)), reps, warmup, per_graph=copies)
+    result.append(dict(kernel="rms_norm (for comparison)", tokens=n, width=width, us=ms * 1e3, gbs=n * width * 6.0 / ms / 1e6))
+    return result
+
+
 def bench_sampling(ops, rows, vocab, stages, reps, warmup):
     """The sampler's truncation pipeline (sort, stages, draw) on ``rows`` rows of ``vocab`` logits;
     wall time with a synchronize on both sides (the call makes dozens of small launches)."""
@@ -272,7 +376,11 @@ def bench_sampling(ops, rows, vocab, stages, reps, warmup):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m leone_b200.kernel_bench")
     ap.add_argument("what", choices=["gemm", "decode-attention", "prefill-attention", "layer-shapes", "sampling",
-                                     "masked-attention"])
+                                     "masked-attention", "pooled-attention", "conv-gru"])
+    ap.add_argument("--pool", type=int, default=64, help="pooled-attention: positions per pooled block")
+    ap.add_argument("--taps", type=int, default=4, help="pooled-attention, conv-gru: taps of the short convolutions")
+    ap.add_argument("--width", type=int, default=2048, help="conv-gru: channels")
+    ap.add_argument("--chunk", type=int, default=None, help="conv-gru: tokens per chunk of the recurrence (default: the part's)")
     ap.add_argument("--mask", choices=["causal", "window", "chunk"], default="window")
     ap.add_argument("--mask-size", type=int, default=1024)
     ap.add_argument("--weights", choices=["softmax", "softmax_plus_one", "sigmoid"], default="sigmoid")
@@ -360,6 +468,14 @@ def main(argv=None) -> int:
         rows.append(bench_masked_attention(ops, args.tokens, args.batch if args.decode else 0, args.context, args.heads,
                                            args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.mask,
                                            args.mask_size, args.weights, args.page_tokens, args.reps, args.warmup))
+    elif args.what == "pooled-attention":
+        rows += bench_pooled_attention(ops, args.tokens, args.batch if args.decode else 0, args.context, args.heads,
+                                       args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.mask_size,
+                                       args.pool, args.page_tokens, args.reps, args.warmup, args.taps)
+    elif args.what == "conv-gru":
+        from .parts.min_gru import DEFAULT_CHUNK
+        rows += bench_conv_and_gru(ops, args.tokens, args.batch if args.decode else 0, args.width, args.taps,
+                                   args.chunk or DEFAULT_CHUNK, args.reps, args.warmup)
     elif args.what == "decode-attention":
         rows.append(bench_decode_attention(ops, args.batch, args.context, args.heads, args.kv_heads,
                                            args.head_dim, args.page_tokens, args.reps, args.warmup, flush, args.prep))

@@ -6,7 +6,9 @@ output is ``out_scale * W_o (S_t * silu(W_g x))`` added to the residual stream. 
 ``[width]`` is fp32, starts at zero and lives in the request's state slot between steps.  The three
 input projections are one product with fp32 results; gates, candidate and state are fp32.  The
 recurrence is linear in ``S``, so prompt portions longer than ``2 chunk`` tokens are cut into chunks
-that run side by side (per-chunk sums, a pass over the chunks, then the outputs).
+that run side by side (per-chunk sums, a pass over the chunks, then the outputs).  Chunks are short:
+a thread walks a chunk's tokens one after the other, and a prompt of a few thousand tokens should
+still give every SM several blocks.
 
 (Feng et al., "Were RNNs All We Needed?" describes minGRU and this candidate function.)
 """
@@ -18,6 +20,9 @@ from ..registry import MIXERS
 from .base import FixedState, Mixer, WeightSpec
 
 
+DEFAULT_CHUNK = 16
+
+
 @MIXERS.register("min_gru")
 class MinGRU(Mixer):
     def __init__(self, params, rt):
@@ -25,7 +30,7 @@ class MinGRU(Mixer):
         self.hidden = int(params["hidden_size"])
         self.width = int(params["width"])
         self.out_scale = float(params.get("out_scale", 1.0))
-        self.chunk = int(params.get("chunk", 64))
+        self.chunk = int(params.get("chunk", DEFAULT_CHUNK))
         self.names = {k: params.get(f"{k}_name", k) for k in ("z", "x", "g", "o")}
         self.bias_names = {k: params.get(f"{k}_bias_name", f"{k}.b") for k in ("z", "x")}
         self.w_in = self.w_o = self.z_bias = self.x_bias = None

@@ -368,19 +368,23 @@ def _step_ctx(q_lens, ctx_lens, slots, dev="cuda:0"):
 @pytest.mark.parametrize("taps", [1, 2, 4, 7])
 def test_short_convolution_with_state_against_the_plain_sum(taps):
     """Two sequences cut into steps of unequal sizes (steps of one token, steps shorter than the taps):
-    the convolution reads what earlier steps left in the state, and zeros before a sequence's start."""
+    the convolution reads what earlier steps left in the state, and zeros before a sequence's start.
+    Then steps of more than a hundred tokens, which a kernel takes that forms eight tokens a thread:
+    a sequence that ends inside such a group, one that starts from the state inside it."""
     from leone_b200.ops.cuda import CudaOps
     g = torch.Generator().manual_seed(taps)
-    channels, lens = 70, [23, 9]
+    channels = 70
     w = torch.randn(channels, taps, generator=g)
-    xs = [torch.randn(n, channels, generator=g) for n in lens]
-    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
+    for lens, cuts in (([23, 9], ([1, 3], [2, 1], [1, 0], [8, 5], [11, 0])),
+                       ([310, 214], ([3, 2], [133, 67], [1, 1], [0, 144], [173, 0]))):
+      xs = [torch.randn(n, channels, generator=g) for n in lens]
+      for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
         ops = CudaOps("cuda:0", dtype)
         for add_input in (False, True):
             state = torch.full((3, max(taps - 1, 0), channels), 7.0, device="cuda:0")
             state[[2, 0]] = 0.0                                   # the slots of the two sequences start from zeros
             done, got = [0, 0], [[], []]
-            for cut in ([1, 3], [2, 1], [1, 0], [8, 5], [11, 0]):
+            for cut in cuts:
                 seqs = [s for s in (0, 1) if cut[s]]
                 ctx, starts = _step_ctx([cut[s] for s in seqs], [done[s] + cut[s] for s in seqs], [(2, 0)[s] for s in seqs])
                 x = torch.cat([xs[s][done[s]:done[s] + cut[s]] for s in seqs]).to(dtype).cuda()
