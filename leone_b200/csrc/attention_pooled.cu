@@ -136,30 +136,34 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
 }
 
 constexpr int kBlockMeanThreads = 256, kBlockMeanWarps = kBlockMeanThreads / 32, kBlockMeanSlab = 512;
+constexpr int kBlockMeanScan = 32;     // tokens of the step that one thread block looks through
 
-// The eight warps of a block take every eighth row of the pooled block each, lanes over columns (in
-// slabs of kBlockMeanSlab); the warps' sums meet in shared memory in ascending order.
+// A thread block looks through kBlockMeanScan tokens of the step for those that end a pooled block
+// (one in `pool`).  For such a token its eight warps take every eighth row of the pooled block each,
+// lanes over columns (in slabs of kBlockMeanSlab); the warps' sums meet in shared memory in ascending order.
 template <typename T>
 __global__ void __launch_bounds__(kBlockMeanThreads)
 attention_pool_blocks_kernel(const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                              const int* __restrict__ block_table, int table_width, int num_pages, int page_tokens,
                              T* __restrict__ kb_pool, T* __restrict__ vb_pool, const int* __restrict__ pool_table,
                              int pool_table_width, int pool_pages, int pool_rows, const int* __restrict__ positions,
-                             const int* __restrict__ seq_of_token, int n_seqs, int n_kv, int dk, int dv, int pool,
-                             int* status) {
+                             const int* __restrict__ seq_of_token, int n_tokens, int n_seqs, int n_kv, int dk, int dv,
+                             int pool, int* status) {
   pdl_trigger();
   pdl_wait();
   __shared__ float part[kBlockMeanWarps][kBlockMeanSlab];
   __shared__ int bad;
-  const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int t_end = min((int)(blockIdx.x + 1) * kBlockMeanScan, n_tokens);
+  for (int t = blockIdx.x * kBlockMeanScan; t < t_end; ++t) {              // every branch below is block-uniform
   const int pos = positions[t], s = seq_of_token[t];
-  if (pos < 0 || s < 0 || s >= n_seqs) return;               // the preparation reported it
-  if ((pos + 1) % pool != 0) return;                         // this token ends no block
+  if (pos < 0 || s < 0 || s >= n_seqs) continue;             // the preparation reported it
+  if ((pos + 1) % pool != 0) continue;                       // this token ends no block
   const int blk = pos / page_tokens;
   const int dst_page = blk < pool_table_width ? pool_table[(size_t)s * pool_table_width + blk] : -1;
   if (dst_page < 0 || dst_page >= pool_pages) {
     if (tid == 0) set_status(status, kBadPage, t, dst_page, pos);
-    return;
+    continue;
   }
   if (tid == 0) bad = 0;
   __syncthreads();
@@ -202,6 +206,7 @@ attention_pool_blocks_kernel(const T* __restrict__ k_pool, const T* __restrict__
       }
     }
     __syncthreads();
+  }
   }
 }
 
@@ -372,11 +377,11 @@ extern "C" int leone_attention_pool_blocks(int dtype, const void* k_pool, const 
   if (dk <= 0 || dv <= 0 || n_kv <= 0 || n_kv > 65535 || pool <= 0 || page_tokens <= 0 || pool_rows <= 0 ||
       pool_rows < (page_tokens + pool - 1) / pool)
     return kRefusedSize;
-  const dim3 grid(n_tokens, n_kv);
+  const dim3 grid((n_tokens + kBlockMeanScan - 1) / kBlockMeanScan, n_kv);
 #define LAUNCH(T)                                                                                                    \
   return launch_kernel(attention_pool_blocks_kernel<T>, grid, dim3(kBlockMeanThreads), 0, stream, (const T*)k_pool, (const T*)v_pool, \
                        block_table, table_width, num_pages, page_tokens, (T*)kb_pool, (T*)vb_pool, pool_table,       \
-                       pool_table_width, pool_pages, pool_rows, positions, seq_of_token, n_seqs, n_kv, dk, dv, pool,  \
+                       pool_table_width, pool_pages, pool_rows, positions, seq_of_token, n_tokens, n_seqs, n_kv, dk, dv, pool, \
                        status)
   if (dtype == 0) LAUNCH(float);
   if (dtype == 1) LAUNCH(__nv_bfloat16);

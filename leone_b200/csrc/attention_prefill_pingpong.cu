@@ -126,6 +126,21 @@ struct Rules {
   const float* bias;
 };
 
+// Pooled blocks before the window (kernel form 2; `window` > 0, ordinary softmax): the query at
+// position p also sees, for every block b of `pool` positions with b pool + pool - 1 <= p - window, one
+// mean key and value.  The means live in pools of their own: the page of a block's last position e
+// (found through pool_table like a token's page) holds its row at (e % page_tokens) / pool, and a page
+// has pool_rows rows.  The block rows come first, as key tiles of their own (block t 128 + r in row r
+// of tile t), then the token tiles; blocks and tokens share the row's running maximum and sum.  The
+// output is multiplied by out_scale.
+struct Pooled {
+  const __nv_bfloat16* kb_pool;
+  const __nv_bfloat16* vb_pool;
+  const int* pool_table;
+  int pool_table_width, pool_pages, pool_rows, pool;
+  float out_scale;
+};
+
 // Byte offset of 16-byte chunk `chunk` (8 elements) of row `row` in a tile of rows of D
 // elements stored as D/64 swizzled halves of [128 rows x 128 bytes].
 __device__ __forceinline__ uint32_t swizzled(int row, int chunk) {
@@ -185,14 +200,16 @@ template <int D> constexpr int smem_bytes() {
   return 2 * kRows * D * 2 + 4 * kKeys * D * 2 + 2 * 2 * kKeys * 8 + 16 * 8 + 1024;
 }
 
-// kRules = false: the reference's layer; the rules are then compile-time constants and the kernel is
-// the one it was before they became parameters.
-template <int D, bool kRules>
+// kForm 0: the reference's layer; the rules are then compile-time constants and the kernel is
+// the one it was before they became parameters.  1: the rules are run-time fields.  2: pooled blocks
+// before a window (ordinary softmax; `pooled` is read in this form only).
+template <int D, int kForm>
 __global__ void __launch_bounds__(kBlockThreads)
 attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row_stride,
                                   __nv_bfloat16* __restrict__ out, int out_stride, PagedArgs pa,
                                   const int* __restrict__ q_start, const int* __restrict__ ctx_len, int n_q,
-                                  float scale, int window, Rules rules_in, int* status) {
+                                  float scale, int window, Rules rules_in, Pooled pooled, int* status) {
+  constexpr bool kRules = kForm == 1, kPooled = kForm == 2;
   struct {
     int weights, chunk;
     const float* bias;
@@ -259,10 +276,16 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
     if (window > 0) k_lo = max(0, start + tok0 - window + 1);
     if (rules.chunk > 0) k_lo = ((start + tok0) / rules.chunk) * rules.chunk;
     const int tile0 = (k_lo / kKeys) * kKeys;
-    const int n0 = (start + hi0 - tile0 + kKeys - 1) / kKeys;
-    const int n1 = hi1 > lo1 ? (start + hi1 - tile0 + kKeys - 1) / kKeys : 0;
-    const int n_tiles = max(n0, n1);
     const int k_hi = start + max(hi0, hi1);             // one past the last key any row reads
+    // pooled form: the row at position p sees the blocks 0 .. blocks_seen(p) - 1; nb_max of them are seen by
+    // the block's last row, in nbt tiles that run before the token tiles (tile t < nbt holds blocks, tile
+    // t >= nbt the keys from tile0 + (t - nbt) * kKeys on)
+    auto blocks_seen = [&](int p) { return kPooled && p >= window - 1 ? (p - window + 1) / pooled.pool : 0; };
+    const int nb_max = blocks_seen(k_hi - 1);
+    const int nbt = kPooled ? (nb_max + kKeys - 1) / kKeys : 0;
+    const int n0 = nbt + (start + hi0 - tile0 + kKeys - 1) / kKeys;
+    const int n1 = hi1 > lo1 ? nbt + (start + hi1 - tile0 + kKeys - 1) / kKeys : 0;
+    const int n_tiles = max(n0, n1);
 
     if (warp == kMmaWarp) {
       // ---------------- the warp that issues the tensor-core work ----------------
@@ -322,6 +345,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
       const bool values = lt >= kStreamThreads;
       const int st = lt & (kStreamThreads - 1);
       const __nv_bfloat16* pool = values ? pa.v_pool : pa.k_pool;
+      const __nv_bfloat16* block_pool = kPooled ? (values ? pooled.vb_pool : pooled.kb_pool) : nullptr;
       const uint32_t tiles = values ? v_t : k_t;
       const uint32_t bar_full = values ? bar_v_full : bar_k_full, bar_free = values ? bar_v_free : bar_k_free;
       long long* rs = row_src + (values ? 2 * kKeys : 0);
@@ -330,7 +354,16 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
       // read a tile ahead (-1: no key here, -2: outside the table)
       auto page_of = [&](int t, int r) {
         int page = -1;
-        const int kj = tile0 + t * kKeys + r;
+        if (kPooled && t < nbt) {                        // row r of a tile of blocks: block t * kKeys + r
+          const int bj = t * kKeys + r;
+          if (bj < nb_max) {
+            const int blk = (bj * pooled.pool + pooled.pool - 1) / pa.page_tokens;
+            page = blk < pooled.pool_table_width ? pooled.pool_table[(size_t)seq * pooled.pool_table_width + blk] : -2;
+            if (page < 0) page = -2;
+          }
+          return page;
+        }
+        const int kj = tile0 + (t - nbt) * kKeys + r;
         if (t < n_tiles && kj < k_hi && kj >= k_lo) {
           const int blk = kj / pa.page_tokens;
           page = blk < pa.table_width ? pa.block_table[(size_t)seq * pa.table_width + blk] : -2;
@@ -339,8 +372,15 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         return page;
       };
       auto source_of = [&](int t, int r, int page) {
-        const int kj = tile0 + t * kKeys + r;
         long long src = -1;
+        if (kPooled && t < nbt) {
+          const int e = (t * kKeys + r) * pooled.pool + pooled.pool - 1;      // the block's last position
+          if (page >= pooled.pool_pages || page == -2) set_status(status, kBadPage, q0 + tok0, page, e);
+          else if (page >= 0)
+            src = (((long long)page * pa.n_kv + kvh) * pooled.pool_rows + (e % pa.page_tokens) / pooled.pool) * D;
+          return src;
+        }
+        const int kj = tile0 + (t - nbt) * kKeys + r;
         if (page >= pa.num_pages || page == -2) set_status(status, kBadPage, q0 + tok0, page, kj);
         else if (page >= 0) src = (((long long)page * pa.n_kv + kvh) * pa.page_tokens + (kj % pa.page_tokens)) * D;
         return src;
@@ -366,11 +406,12 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         named_barrier_sync(bar_id, kStreamThreads);      // the row sources of tile t are all written
         const uint32_t dst = tiles + (t & 1) * kTileBytes;
         const uint32_t d0 = dst + swizzled(r0, ch0), d1 = dst + swizzled(r0, ch0 + 1);
+        const __nv_bfloat16* from = kPooled && t < nbt ? block_pool : pool;
 #pragma unroll
         for (int i = 0; i < kKeys / kStep; ++i) {
           const long long src = rs_t[r0 + i * kStep];
           const bool ok = src >= 0;
-          const __nv_bfloat16* p = ok ? pool + src + ch0 * 8 : pool;
+          const __nv_bfloat16* p = ok ? from + src + ch0 * 8 : pool;
           cp_async16(d0 + i * kStep * 128, p, ok);
           cp_async16(d1 + i * kStep * 128, ok ? p + 8 : pool, ok);
         }
@@ -390,6 +431,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
       const int my_tl = row / g;
       const int my_pos = (my_tl < tq && lo + my_tl < hi) ? start + lo + my_tl : -1;   // -1: row unused
       const int first_pos = start + lo, last_pos = start + hi - 1;
+      const int my_blocks = my_pos >= 0 ? blocks_seen(my_pos) : 0;          // pooled form: this row sees that many blocks
       const float my_bias = rules.weights == 2 ? rules.bias[kvh * g + (row - my_tl * g)] * kLog2e : 0.f;
       const float sl2 = (rules.weights == 2 ? -scale : scale) * kLog2e;      // (see `shift` below)
       const uint32_t t_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);      // this warp's lanes
@@ -418,21 +460,28 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         if (lane == 0) mbar_arrive(bar_q);
       }
       for (int t = 0; t < nj; ++t) {
-        const int tile_start = tile0 + t * kKeys + half * 64;     // this thread's first key
+        const bool block_tile = kPooled && t < nbt;
+        const int tk = t - nbt;                                   // the tile's number among the token tiles
+        // this thread's first key (in a tile of blocks: its first block)
+        const int tile_start = block_tile ? t * kKeys + half * 64 : tile0 + tk * kKeys + half * 64;
         // S_j(t) is complete, and so is PV_j(t - 1): O_j is at rest until this tile's go-ahead
         if (ok_all && !mbar_wait_long(bar_s + 8 * j, t & 1, giveup)) ok_all = false;
         tc_fence_after();
         // A tile that every row of this query tile sees whole needs no masking (the same for all
         // threads, so the branch is uniform; rows that stand for no token compute on zeros and
         // are never stored).
-        const bool all_visible = tile0 + (t + 1) * kKeys - 1 <= first_pos &&
-                                 (window <= 0 || tile0 + t * kKeys > last_pos - window) &&
-                                 (rules.chunk <= 0 || tile0 + t * kKeys >= (last_pos / rules.chunk) * rules.chunk);
-        // keys first .. first + span (relative to this thread's first key) are visible to this row
-        const int first = window > 0 ? max(my_pos - window + 1 - tile_start, 0)
+        const bool all_visible =
+            block_tile ? (t + 1) * kKeys <= blocks_seen(first_pos)
+                       : tile0 + (tk + 1) * kKeys - 1 <= first_pos && (window <= 0 || tile0 + tk * kKeys > last_pos - window) &&
+                             (rules.chunk <= 0 || tile0 + tk * kKeys >= (last_pos / rules.chunk) * rules.chunk);
+        // keys first .. first + span (relative to this thread's first key) are visible to this row;
+        // of a tile of blocks the row sees those below my_blocks
+        const int last_seen = block_tile ? my_blocks - 1 : my_pos;
+        const int first = block_tile ? 0
+                          : window > 0 ? max(my_pos - window + 1 - tile_start, 0)
                           : (rules.chunk > 0 ? max((max(my_pos, 0) / rules.chunk) * rules.chunk - tile_start, 0) : 0);
-        const unsigned span = my_pos >= 0 && my_pos - tile_start >= first ? (unsigned)(my_pos - tile_start - first) : 0u;
-        const bool none = my_pos < 0 || my_pos - tile_start < first;      // no key of this thread's columns is visible
+        const unsigned span = my_pos >= 0 && last_seen - tile_start >= first ? (unsigned)(last_seen - tile_start - first) : 0u;
+        const bool none = my_pos < 0 || last_seen - tile_start < first;   // no key of this thread's columns is visible
         // pass 1: the maximum over the keys the row may see; four running maxima (the chain of
         // dependent instructions is a quarter as long).  The 64 scores come in two loads of 32
         // that are both in flight at once: a load takes a few hundred cycles to come back.
@@ -552,7 +601,7 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
         if (rules.weights == 1) l_row += ex2(m_run == -INFINITY ? 0.f : -m_run);      // the silent member's share
         if (ok_all && !mbar_wait_long(bar_o + 8 * j, 0, giveup)) ok_all = false;
         tc_fence_after();
-        const float inv = rules.weights == 2 ? 1.f : (l_row > 0.f ? 1.f / l_row : 0.f);
+        const float inv = (rules.weights == 2 ? 1.f : (l_row > 0.f ? 1.f / l_row : 0.f)) * (kPooled ? pooled.out_scale : 1.f);
         const bool store = ok_all && my_pos >= 0;
         const int hh = row - my_tl * g;
         __nv_bfloat16* dst = out + (size_t)(q0 + lo + (store ? my_tl : 0)) * out_stride + (size_t)(kvh * g + hh) * D +
@@ -590,13 +639,13 @@ attention_prefill_pingpong_kernel(const __nv_bfloat16* __restrict__ qkv, int row
   }
 }
 
-template <int D, bool kRules>
+template <int D, int kForm>
 int launch_form(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride, const PagedArgs& pa,
                 const int* q_start, const int* ctx_len, int n_seqs, int n_q, int max_q_len, float scale, int window,
-                const Rules& rules, int* status, cudaStream_t stream) {
+                const Rules& rules, const Pooled& pooled, int* status, cudaStream_t stream) {
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_pingpong_kernel<D, kRules>,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_pingpong_kernel<D, kForm>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes<D>());
     if (e != cudaSuccess) return (int)e;
     configured = true;
@@ -604,19 +653,22 @@ int launch_form(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, in
   const int g = n_q / pa.n_kv;
   const int tq = kRows / g;
   dim3 grid(((max_q_len + 2 * tq - 1) / (2 * tq)) * pa.n_kv, 1, n_seqs);
-  return launch_kernel(attention_prefill_pingpong_kernel<D, kRules>, grid, dim3(kBlockThreads), smem_bytes<D>(), stream,
-                       qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, rules, status);
+  return launch_kernel(attention_prefill_pingpong_kernel<D, kForm>, grid, dim3(kBlockThreads), smem_bytes<D>(), stream,
+                       qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_q, scale, window, rules, pooled, status);
 }
 
 template <int D>
 int launch(const __nv_bfloat16* qkv, int row_stride, __nv_bfloat16* out, int out_stride, const PagedArgs& pa,
            const int* q_start, const int* ctx_len, int n_seqs, int n_q, int max_q_len, float scale, int window,
-           const Rules& rules, int* status, cudaStream_t stream) {
+           const Rules& rules, const Pooled& pooled, int* status, cudaStream_t stream) {
+  if (pooled.pool > 0)
+    return launch_form<D, 2>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, max_q_len, scale, window,
+                             rules, pooled, status, stream);
   if (rules.weights != 0 || rules.chunk != 0)
-    return launch_form<D, true>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, max_q_len, scale,
-                                window, rules, status, stream);
-  return launch_form<D, false>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, max_q_len, scale,
-                               window, rules, status, stream);
+    return launch_form<D, 1>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, max_q_len, scale, window,
+                             rules, pooled, status, stream);
+  return launch_form<D, 0>(qkv, row_stride, out, out_stride, pa, q_start, ctx_len, n_seqs, n_q, max_q_len, scale, window,
+                           rules, pooled, status, stream);
 }
 
 }  // namespace pingpong
@@ -646,11 +698,44 @@ extern "C" int leone_attention_prefill_pingpong_rules(const void* qkv, int row_s
   if (((uintptr_t)qkv | (uintptr_t)out | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) return kRefusedAlignment;
   pingpong::PagedArgs pa{(const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table, table_width,
                          page_tokens, num_pages, n_kv};
+  const pingpong::Pooled none{nullptr, nullptr, nullptr, 0, 0, 0, 0, 1.f};
   if (d == 64)
     return pingpong::launch<64>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, out_stride, pa, q_start,
-                                ctx_len, n_seqs, n_q, max_q_len, scale, window, rules, status, stream);
+                                ctx_len, n_seqs, n_q, max_q_len, scale, window, rules, none, status, stream);
   return pingpong::launch<128>((const __nv_bfloat16*)qkv, row_stride, (__nv_bfloat16*)out, out_stride, pa, q_start,
-                               ctx_len, n_seqs, n_q, max_q_len, scale, window, rules, status, stream);
+                               ctx_len, n_seqs, n_q, max_q_len, scale, window, rules, none, status, stream);
+}
+
+// The same kernel with pooled blocks before the window (pingpong::Pooled): q rows of n_q heads of d
+// elements, keys and values of d elements in the token pools and in the pools of block means.
+extern "C" int leone_attention_prefill_pingpong_pooled(const void* q, int row_stride, void* out, int out_stride,
+                                                       const void* k_pool, const void* v_pool, const int* block_table,
+                                                       int table_width, int num_pages, int page_tokens,
+                                                       const void* kb_pool, const void* vb_pool, const int* pool_table,
+                                                       int pool_table_width, int pool_pages, int pool_rows,
+                                                       const int* q_start, const int* ctx_len, int n_seqs, int max_q_len,
+                                                       int n_q, int n_kv, int d, float scale, int window, int pool,
+                                                       float out_scale, int* status, cudaStream_t stream) {
+  if (n_seqs <= 0 || max_q_len <= 0) return 0;
+  if (window <= 0 || pool <= 0 || !(scale > 0.f) || kb_pool == nullptr || vb_pool == nullptr || pool_table == nullptr ||
+      pool_table_width <= 0 || pool_rows < (page_tokens + pool - 1) / pool)
+    return kRefusedSize;
+  if (d != 64 && d != 128) return kRefusedSize;
+  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || n_q / n_kv > pingpong::kRows) return kRefusedSize;
+  if (page_tokens <= 0 || table_width <= 0 || n_seqs > 65535) return kRefusedSize;
+  if (row_stride % 8 != 0 || out_stride % 8 != 0) return kRefusedAlignment;
+  if (((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)kb_pool | (uintptr_t)vb_pool) & 15)
+    return kRefusedAlignment;
+  pingpong::PagedArgs pa{(const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, block_table, table_width,
+                         page_tokens, num_pages, n_kv};
+  const pingpong::Rules rules{0, 0, nullptr};
+  const pingpong::Pooled pooled{(const __nv_bfloat16*)kb_pool, (const __nv_bfloat16*)vb_pool, pool_table,
+                                pool_table_width, pool_pages, pool_rows, pool, out_scale};
+  if (d == 64)
+    return pingpong::launch<64>((const __nv_bfloat16*)q, row_stride, (__nv_bfloat16*)out, out_stride, pa, q_start, ctx_len,
+                                n_seqs, n_q, max_q_len, scale, window, rules, pooled, status, stream);
+  return pingpong::launch<128>((const __nv_bfloat16*)q, row_stride, (__nv_bfloat16*)out, out_stride, pa, q_start, ctx_len,
+                               n_seqs, n_q, max_q_len, scale, window, rules, pooled, status, stream);
 }
 
 extern "C" int leone_attention_prefill_pingpong(const void* qkv, int row_stride, void* out, int out_stride,

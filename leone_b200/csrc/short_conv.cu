@@ -57,21 +57,62 @@ short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w
   out[(size_t)t * ldo + c] = from_float<TO>(acc);
 }
 
-// The same for kConvTile consecutive tokens of a channel per thread (steps of many tokens): where the
-// tile's tokens belong to one sequence, the kConvTile + taps - 1 inputs they read are loaded once and
-// every output is formed from registers; a tile that spans sequences falls back to token-by-token.
+// The same for kConvTile consecutive tokens of V neighbouring channels per thread (steps of many
+// tokens): where the tile's tokens belong to one sequence, the kConvTile + taps - 1 inputs they read
+// are loaded once (V = 4: as 16- or 8-byte vectors) and every output is formed from registers; a tile
+// that spans sequences falls back to token-by-token.  kT is the most taps the form takes (its
+// register arrays are sized by it).  Per channel the sum is the one of short_conv_kernel, in the same order.
 constexpr int kConvTile = 8;
 
-template <typename TI, typename TO>
+template <typename T, int V> struct ConvVec;
+template <> struct ConvVec<float, 1> {
+  static __device__ __forceinline__ void load(const float* p, float* v) { v[0] = *p; }
+  static __device__ __forceinline__ void store(float* p, const float* v) { *p = v[0]; }
+};
+template <> struct ConvVec<__nv_bfloat16, 1> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) { v[0] = __bfloat162float(*p); }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) { *p = __float2bfloat16_rn(v[0]); }
+};
+template <> struct ConvVec<float, 4> {
+  static __device__ __forceinline__ void load(const float* p, float* v) {
+    const float4 r = *reinterpret_cast<const float4*>(p);
+    v[0] = r.x, v[1] = r.y, v[2] = r.z, v[3] = r.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* v) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+  }
+};
+template <> struct ConvVec<__nv_bfloat16, 4> {
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* v) {
+    const uint2 r = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&r.x), b = *reinterpret_cast<const __nv_bfloat162*>(&r.y);
+    v[0] = __low2float(a), v[1] = __high2float(a), v[2] = __low2float(b), v[3] = __high2float(b);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    uint2 r;
+    r.x = *reinterpret_cast<const uint32_t*>(&a);
+    r.y = *reinterpret_cast<const uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = r;
+  }
+};
+
+template <typename TI, typename TO, int V, int kT>
 __global__ void __launch_bounds__(kConvThreads)
 short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ state,
                        TO* __restrict__ out, int ldo, const int* __restrict__ q_start,
                        const int* __restrict__ seq_of_token, const int* __restrict__ slot_ids, int n_tokens, int channels,
                        int taps, int add_input, int n_seqs, int n_slots, int* status) {
   pdl_trigger();
-  pdl_wait();
-  const int t0 = blockIdx.x * kConvTile, c = blockIdx.y * kConvThreads + threadIdx.x;
+  const int t0 = blockIdx.x * kConvTile, c = (blockIdx.y * kConvThreads + threadIdx.x) * V;
   if (c >= channels) return;
+  // the weights are not written during a step: fetched before the wait for the kernel ahead
+  float wt[kT][V];
+#pragma unroll
+  for (int j = 0; j < kT; ++j)
+#pragma unroll
+    for (int e = 0; e < V; ++e) wt[j][e] = j < taps ? w[(size_t)(c + e) * taps + j] : 0.f;
+  pdl_wait();
   const int t_end = min(t0 + kConvTile, n_tokens);
   const int s0 = seq_of_token[t0], s1 = seq_of_token[t_end - 1];
   if (s0 == s1 && s0 >= 0 && s0 < n_seqs) {
@@ -82,39 +123,43 @@ short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restric
     }
     const int local0 = t0 - q_start[s0];
     const float* st = state + (size_t)slot * (taps - 1) * channels;
-    float v[kConvTile + kMaxTaps - 1];
+    float v[kConvTile + kT - 1][V];
     // input r of the tile is the sequence's token local0 - (taps - 1) + r of this step, or a state row before it
 #pragma unroll
-    for (int r = 0; r < kConvTile + kMaxTaps - 1; ++r) {
-      v[r] = 0.f;
+    for (int r = 0; r < kConvTile + kT - 1; ++r) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) v[r][e] = 0.f;
       if (r < kConvTile + taps - 1) {
         const int i = local0 - (taps - 1) + r;
         if (i >= 0) {
-          if (t0 - (taps - 1) + r < t_end) v[r] = to_float<TI>(x[(size_t)(t0 - (taps - 1) + r) * ldx + c]);
+          if (t0 - (taps - 1) + r < t_end) ConvVec<TI, V>::load(x + (size_t)(t0 - (taps - 1) + r) * ldx + c, v[r]);
         } else {
-          v[r] = st[(size_t)(taps - 1 + i) * channels + c];
+          ConvVec<float, V>::load(st + (size_t)(taps - 1 + i) * channels + c, v[r]);
         }
       }
     }
-    float wt[kMaxTaps];
-#pragma unroll
-    for (int j = 0; j < kMaxTaps; ++j) wt[j] = j < taps ? w[(size_t)c * taps + j] : 0.f;
 #pragma unroll
     for (int i = 0; i < kConvTile; ++i) {
       if (t0 + i < t_end) {
-        float acc = 0.f;
+        float acc[V];
 #pragma unroll
-        for (int j = 0; j < kMaxTaps; ++j)
-          if (j < taps) acc = fmaf(wt[j], v[i + j], acc);
+        for (int e = 0; e < V; ++e) acc[e] = 0.f;
+#pragma unroll
+        for (int j = 0; j < kT; ++j)
+          if (j < taps) {
+#pragma unroll
+            for (int e = 0; e < V; ++e) acc[e] = fmaf(wt[j][e], v[i + j][e], acc[e]);
+          }
         // the token's own input is v[i + taps - 1]: picked by a static index
         if (add_input) {
-          float own = 0.f;
 #pragma unroll
-          for (int j = 0; j < kMaxTaps; ++j)
-            if (j == taps - 1) own = v[i + j];
-          acc += own;
+          for (int j = 0; j < kT; ++j)
+            if (j == taps - 1) {
+#pragma unroll
+              for (int e = 0; e < V; ++e) acc[e] += v[i + j][e];
+            }
         }
-        out[(size_t)(t0 + i) * ldo + c] = from_float<TO>(acc);
+        ConvVec<TO, V>::store(out + (size_t)(t0 + i) * ldo + c, acc);
       }
     }
     return;
@@ -132,15 +177,18 @@ short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restric
     }
     const int local = t - q_start[s];
     const float* st = state + (size_t)slot * (taps - 1) * channels;
-    float acc = 0.f;
-    for (int j = 0; j < taps; ++j) {
-      const int back = taps - 1 - j;
-      const float u = back <= local ? to_float<TI>(x[(size_t)(t - back) * ldx + c])
-                                    : st[(size_t)(taps - 1 + local - back) * channels + c];
-      acc = fmaf(w[(size_t)c * taps + j], u, acc);
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      float acc = 0.f;
+      for (int j = 0; j < taps; ++j) {
+        const int back = taps - 1 - j;
+        const float u = back <= local ? to_float<TI>(x[(size_t)(t - back) * ldx + c + e])
+                                      : st[(size_t)(taps - 1 + local - back) * channels + c + e];
+        acc = fmaf(w[(size_t)(c + e) * taps + j], u, acc);
+      }
+      if (add_input) acc += to_float<TI>(x[(size_t)t * ldx + c + e]);
+      out[(size_t)(t * (size_t)ldo) + c + e] = from_float<TO>(acc);
     }
-    if (add_input) acc += to_float<TI>(x[(size_t)t * ldx + c]);
-    out[(size_t)t * ldo + c] = from_float<TO>(acc);
   }
 }
 
@@ -343,13 +391,21 @@ extern "C" int leone_short_conv(int in_dtype, int out_dtype, const void* x, int 
   if (taps > 1 && state == nullptr) return kRefusedSize;
   const dim3 grid(n_tokens, (channels + kConvThreads - 1) / kConvThreads);
   const bool tiled = n_tokens >= 16 * kConvTile;        // a decode step's tokens each belong to another sequence
+  // four channels a thread where every row starts on a 16-byte boundary and the taps fit the small form
+  const bool vec = tiled && taps <= 4 && channels % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 &&
+                   (((uintptr_t)x | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
   const dim3 tile_grid((n_tokens + kConvTile - 1) / kConvTile, grid.y);
+  const dim3 vec_grid(tile_grid.x, (channels / 4 + kConvThreads - 1) / kConvThreads);
 #define LAUNCH(TI, TO)                                                                                              \
   {                                                                                                                 \
+    if (vec)                                                                                                        \
+      return launch_kernel(short_conv_tile_kernel<TI, TO, 4, 4>, vec_grid, dim3(kConvThreads), 0, stream,           \
+                           (const TI*)x, ldx, w, state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, n_tokens,  \
+                           channels, taps, add_input, n_seqs, n_slots, status);                                     \
     if (tiled)                                                                                                      \
-      return launch_kernel(short_conv_tile_kernel<TI, TO>, tile_grid, dim3(kConvThreads), 0, stream, (const TI*)x,  \
-                           ldx, w, state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, n_tokens, channels, taps, \
-                           add_input, n_seqs, n_slots, status);                                                     \
+      return launch_kernel(short_conv_tile_kernel<TI, TO, 1, kMaxTaps>, tile_grid, dim3(kConvThreads), 0, stream,   \
+                           (const TI*)x, ldx, w, state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, n_tokens,  \
+                           channels, taps, add_input, n_seqs, n_slots, status);                                     \
     return launch_kernel(short_conv_kernel<TI, TO>, grid, dim3(kConvThreads), 0, stream, (const TI*)x, ldx, w,      \
                          state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, channels, taps, add_input, n_seqs,  \
                          n_slots, status);                                                                          \

@@ -806,8 +806,13 @@ class CudaOps:
         the sizes that kernel takes (bfloat16, key and value widths multiples of 16 up to 128).  A
         decode step's members (block rows, then token rows) are split over blocks until the SMs are busy."""
         decode = bool(ctx.decode_only)
-        if (q.dtype != torch.bfloat16 or os.environ.get("LEONE_NO_POOLED_MMA", "0") == "1"
-                or getattr(ctx, "q_start", None) is None
+        if q.dtype != torch.bfloat16 or getattr(ctx, "q_start", None) is None:
+            return False
+        # prompt portions with head sizes 64 and 128 and values as wide as keys: the tcgen05 prompt kernel
+        if (not decode and dk == dv and os.environ.get("LEONE_NO_POOLED_TC", "0") != "1"
+                and self.fast.attention_pooled_window(ctx, q, out, args, n_q, n_kv, dk, scale, window, pool, out_scale)):
+            return True
+        if (os.environ.get("LEONE_NO_POOLED_MMA", "0") == "1"
                 or not self.mixers.leone_attention_masked_mma_supported(n_q, n_kv, dk, dv, 1 if decode else 0)
                 or q.stride(0) % 8 or out.stride(0) % 2):
             return False

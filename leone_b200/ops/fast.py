@@ -575,6 +575,25 @@ class FastKernels:
             raise RuntimeError(f"prompt attention refused or failed with code {code}")
         return True
 
+    def attention_pooled_window(self, ctx, q, out, args, n_q, n_kv, d, scale, window, pool, out_scale) -> bool:
+        """Prompt portions and mixed steps of attention over a window and pooled blocks before it on
+        the tcgen05 prompt kernel (its form with tiles of block means ahead of the token tiles): head
+        sizes 64 and 128 with values as wide as keys.  ``args``: the token pools and the pools of block
+        means as ``CudaOps._pooled_args`` lists them.  False: not this kernel's case."""
+        g = n_q // n_kv
+        if not (self.attention_supported(q.dtype, n_q, n_kv, d, q.stride(0)) and self.use_tc_attention
+                and d in (64, 128) and g <= 128 and q.stride(0) % 8 == 0 and out.stride(0) % 8 == 0
+                and not ctx.decode_only):
+            return False
+        kp, vp, bt, bt_width, pages, page_tokens, kb, vb, pt, pt_width, pool_pages, rows = args
+        code = self.lib.leone_attention_prefill_pingpong_pooled(
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), kp, vp, bt, bt_width, pages, page_tokens, kb, vb, pt, pt_width,
+            pool_pages, rows, _ptr(ctx.q_start), _ptr(ctx.ctx_len), ctx.n_seqs, int(ctx.max_q_len), n_q, n_kv, d,
+            c_float(scale), int(window), int(pool), c_float(out_scale), _ptr(ctx.status), self._stream())
+        if code != 0:
+            raise RuntimeError(f"prompt attention with pooled blocks refused or failed with code {code}")
+        return True
+
     def _attn_scratch(self, floats: int):
         if self._attn_ws is None or self._attn_ws.numel() < floats:
             self._retire(self._attn_ws)

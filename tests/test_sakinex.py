@@ -194,7 +194,7 @@ def test_replay_on_the_gpu(which, dtype, mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("switch", ["LEONE_NO_POOLED_MMA", "LEONE_NO_EXPERT_MMA", "LEONE_NO_TENSOR_CORES", "LEONE_NO_FUSED_NORM"])
+@pytest.mark.parametrize("switch", ["LEONE_NO_POOLED_TC", "LEONE_NO_POOLED_MMA", "LEONE_NO_EXPERT_MMA", "LEONE_NO_TENSOR_CORES", "LEONE_NO_FUSED_NORM"])
 @pytest.mark.parametrize("which", ["C", "D"])
 def test_bfloat16_kernel_switches(which, switch, monkeypatch):
     """Every bfloat16 kernel has an any-size form behind a switch; with the switch thrown the same
@@ -491,7 +491,9 @@ def _paged_sequences(ctx_lens, n_kv, dk, dv, page, pool, dtype, g, dev="cuda:0")
 @pytest.mark.parametrize("n_q,n_kv,dk,dv,window,pool,page", [
     (6, 2, 12, 20, 9, 3, 8), (4, 4, 24, 16, 70, 7, 16), (3, 1, 40, 8, 1, 1, 4), (2, 1, 16, 136, 33, 40, 16),
     (8, 2, 128, 128, 64, 16, 16), (4, 1, 64, 64, 100, 16, 16), (6, 2, 32, 48, 130, 24, 32), (16, 4, 96, 96, 17, 64, 16),
-    (5, 5, 16, 16, 400, 4, 16), (8, 1, 128, 16, 48, 8, 16)])
+    (5, 5, 16, 16, 400, 4, 16), (8, 1, 128, 16, 48, 8, 16),
+    # more than 128 blocks (several tiles of block means on the tcgen05 form), pool 1, a window past the prompt
+    (4, 2, 64, 64, 5, 2, 16), (16, 2, 128, 128, 40, 1, 16), (2, 1, 64, 64, 1, 1, 32), (8, 8, 128, 128, 290, 3, 16)])
 def test_pooled_window_attention_kernels_against_the_plain_rule(n_q, n_kv, dk, dv, window, pool, page):
     """The attention kernels alone over shuffled pages: three sequences of unequal lengths as prompt
     portions that start in the middle of a sequence, and as a decode step, in 32-bit (the any-size
