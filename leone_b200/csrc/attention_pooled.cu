@@ -135,78 +135,99 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
   }
 }
 
-constexpr int kBlockMeanThreads = 256, kBlockMeanWarps = kBlockMeanThreads / 32, kBlockMeanSlab = 512;
-constexpr int kBlockMeanScan = 32;     // tokens of the step that one thread block looks through
+constexpr int kBlockMeanThreads = 256, kBlockMeanWarps = kBlockMeanThreads / 32, kBlockMeanSlab = 256;
+constexpr int kBlockMeanAhead = 8;     // rows of a warp whose loads are issued before their sums
 
-// A thread block looks through kBlockMeanScan tokens of the step for those that end a pooled block
-// (one in `pool`).  For such a token its eight warps take every eighth row of the pooled block each,
-// lanes over columns (in slabs of kBlockMeanSlab); the warps' sums meet in shared memory in ascending order.
+// A thread block looks through `scan` tokens of the step for those that end a pooled block (one in
+// `pool`).  For such a token its eight warps take every eighth row of the pooled block each, lanes over
+// columns (in slabs of kBlockMeanSlab); the warps' sums meet in shared memory in ascending order.  A warp
+// finds the pages of its rows with one look-up per lane and has the loads of kBlockMeanAhead rows in
+// flight at a time; the sums are formed in ascending position whatever the grouping.
 template <typename T>
 __global__ void __launch_bounds__(kBlockMeanThreads)
 attention_pool_blocks_kernel(const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                              const int* __restrict__ block_table, int table_width, int num_pages, int page_tokens,
                              T* __restrict__ kb_pool, T* __restrict__ vb_pool, const int* __restrict__ pool_table,
                              int pool_table_width, int pool_pages, int pool_rows, const int* __restrict__ positions,
-                             const int* __restrict__ seq_of_token, int n_tokens, int n_seqs, int n_kv, int dk, int dv,
-                             int pool, int* status) {
+                             const int* __restrict__ seq_of_token, int n_tokens, int scan, int n_seqs, int n_kv, int dk,
+                             int dv, int pool, int* status) {
   pdl_trigger();
   pdl_wait();
   __shared__ float part[kBlockMeanWarps][kBlockMeanSlab];
   __shared__ int bad;
   const int g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int t_end = min((int)(blockIdx.x + 1) * kBlockMeanScan, n_tokens);
-  for (int t = blockIdx.x * kBlockMeanScan; t < t_end; ++t) {              // every branch below is block-uniform
-  const int pos = positions[t], s = seq_of_token[t];
-  if (pos < 0 || s < 0 || s >= n_seqs) continue;             // the preparation reported it
-  if ((pos + 1) % pool != 0) continue;                       // this token ends no block
-  const int blk = pos / page_tokens;
-  const int dst_page = blk < pool_table_width ? pool_table[(size_t)s * pool_table_width + blk] : -1;
-  if (dst_page < 0 || dst_page >= pool_pages) {
-    if (tid == 0) set_status(status, kBadPage, t, dst_page, pos);
-    continue;
-  }
-  if (tid == 0) bad = 0;
-  __syncthreads();
-  const long long dst = ((long long)dst_page * n_kv + g) * pool_rows + (pos % page_tokens) / pool;
-  const int first = pos - pool + 1, width = dk + dv;
-  for (int c0 = 0; c0 < width; c0 += kBlockMeanSlab) {
-    const int cn = min(kBlockMeanSlab, width - c0);
-    float sum[kBlockMeanSlab / 32];
+  const int t_end = min((int)(blockIdx.x + 1) * scan, n_tokens);
+  for (int t = blockIdx.x * scan; t < t_end; ++t) {          // every branch on t, pos and s is block-uniform
+    const int pos = positions[t], s = seq_of_token[t];
+    if (pos < 0 || s < 0 || s >= n_seqs) continue;           // the preparation reported it
+    if ((pos + 1) % pool != 0) continue;                     // this token ends no block
+    const int blk = pos / page_tokens;
+    const int dst_page = blk < pool_table_width ? pool_table[(size_t)s * pool_table_width + blk] : -1;
+    if (dst_page < 0 || dst_page >= pool_pages) {
+      if (tid == 0) set_status(status, kBadPage, t, dst_page, pos);
+      continue;
+    }
+    if (tid == 0) bad = 0;
+    __syncthreads();
+    const long long dst = ((long long)dst_page * n_kv + g) * pool_rows + (pos % page_tokens) / pool;
+    const int first = pos - pool + 1, width = dk + dv;
+    const int n_w = pool > warp ? (pool - warp + kBlockMeanWarps - 1) / kBlockMeanWarps : 0;    // rows of this warp
+    for (int c0 = 0; c0 < width; c0 += kBlockMeanSlab) {
+      const int cn = min(kBlockMeanSlab, width - c0);
+      float sum[kBlockMeanSlab / 32];
 #pragma unroll
-    for (int i = 0; i < kBlockMeanSlab / 32; ++i) sum[i] = 0.f;
-    for (int j = first + warp; j <= pos; j += kBlockMeanWarps) {
-      const int b = j / page_tokens;
-      const int page = b < table_width ? block_table[(size_t)s * table_width + b] : -1;
-      if (page < 0 || page >= num_pages) {
-        if (lane == 0) {
-          set_status(status, kBadPage, t, page, j);
-          bad = 1;
+      for (int i = 0; i < kBlockMeanSlab / 32; ++i) sum[i] = 0.f;
+      for (int i0 = 0; i0 < n_w; i0 += 32) {
+        // lane l: where row i0 + l of this warp (position first + warp + 8 (i0 + l)) lies in the token pools
+        long long my_at = -1;
+        if (i0 + lane < n_w) {
+          const int j = first + warp + kBlockMeanWarps * (i0 + lane);
+          const int b = j / page_tokens;
+          const int page = b < table_width ? block_table[(size_t)s * table_width + b] : -1;
+          if (page < 0 || page >= num_pages) {
+            set_status(status, kBadPage, t, page, j);
+            bad = 1;
+          } else {
+            my_at = ((long long)page * n_kv + g) * page_tokens + (j % page_tokens);
+          }
         }
-        continue;
-      }
-      const long long at = ((long long)page * n_kv + g) * page_tokens + (j % page_tokens);
+        const int n_here = min(32, n_w - i0);
+        for (int r0 = 0; r0 < n_here; r0 += kBlockMeanAhead) {
+          float val[kBlockMeanAhead][kBlockMeanSlab / 32];
 #pragma unroll
-      for (int i = 0; i < kBlockMeanSlab / 32; ++i) {
-        const int c = c0 + lane + 32 * i;
-        if (lane + 32 * i < cn) sum[i] += c < dk ? to_float<T>(k_pool[at * dk + c]) : to_float<T>(v_pool[at * dv + (c - dk)]);
+          for (int u = 0; u < kBlockMeanAhead; ++u) {
+            const long long at = __shfl_sync(0xffffffffu, my_at, min(r0 + u, n_here - 1));
+            const bool use = r0 + u < n_here && at >= 0;
+#pragma unroll
+            for (int i = 0; i < kBlockMeanSlab / 32; ++i) {
+              const int c = c0 + lane + 32 * i;
+              val[u][i] = 0.f;
+              if (use && lane + 32 * i < cn)
+                val[u][i] = c < dk ? to_float<T>(k_pool[at * dk + c]) : to_float<T>(v_pool[at * dv + (c - dk)]);
+            }
+          }
+#pragma unroll
+          for (int u = 0; u < kBlockMeanAhead; ++u)
+#pragma unroll
+            for (int i = 0; i < kBlockMeanSlab / 32; ++i) sum[i] += val[u][i];     // a row past the end adds 0
+        }
       }
+#pragma unroll
+      for (int i = 0; i < kBlockMeanSlab / 32; ++i)
+        if (lane + 32 * i < cn) part[warp][lane + 32 * i] = sum[i];
+      __syncthreads();
+      if (!bad) {
+        for (int cc = tid; cc < cn; cc += kBlockMeanThreads) {
+          float total = 0.f;
+#pragma unroll
+          for (int w = 0; w < kBlockMeanWarps; ++w) total += part[w][cc];
+          const int c = c0 + cc;
+          if (c < dk) kb_pool[dst * dk + c] = from_float<T>(total / (float)pool);
+          else vb_pool[dst * dv + (c - dk)] = from_float<T>(total / (float)pool);
+        }
+      }
+      __syncthreads();
     }
-#pragma unroll
-    for (int i = 0; i < kBlockMeanSlab / 32; ++i)
-      if (lane + 32 * i < cn) part[warp][lane + 32 * i] = sum[i];
-    __syncthreads();
-    if (!bad) {
-      for (int cc = tid; cc < cn; cc += kBlockMeanThreads) {
-        float total = 0.f;
-#pragma unroll
-        for (int w = 0; w < kBlockMeanWarps; ++w) total += part[w][cc];
-        const int c = c0 + cc;
-        if (c < dk) kb_pool[dst * dk + c] = from_float<T>(total / (float)pool);
-        else vb_pool[dst * dv + (c - dk)] = from_float<T>(total / (float)pool);
-      }
-    }
-    __syncthreads();
-  }
   }
 }
 
@@ -377,11 +398,13 @@ extern "C" int leone_attention_pool_blocks(int dtype, const void* k_pool, const 
   if (dk <= 0 || dv <= 0 || n_kv <= 0 || n_kv > 65535 || pool <= 0 || page_tokens <= 0 || pool_rows <= 0 ||
       pool_rows < (page_tokens + pool - 1) / pool)
     return kRefusedSize;
-  const dim3 grid((n_tokens + kBlockMeanScan - 1) / kBlockMeanScan, n_kv);
+  // a long step: a thread block looks through several tokens, of which one in `pool` ends a block
+  const int scan = n_tokens >= 4096 ? 32 : (n_tokens >= 512 ? 8 : 1);
+  const dim3 grid((n_tokens + scan - 1) / scan, n_kv);
 #define LAUNCH(T)                                                                                                    \
   return launch_kernel(attention_pool_blocks_kernel<T>, grid, dim3(kBlockMeanThreads), 0, stream, (const T*)k_pool, (const T*)v_pool, \
                        block_table, table_width, num_pages, page_tokens, (T*)kb_pool, (T*)vb_pool, pool_table,       \
-                       pool_table_width, pool_pages, pool_rows, positions, seq_of_token, n_tokens, n_seqs, n_kv, dk, dv, pool, \
+                       pool_table_width, pool_pages, pool_rows, positions, seq_of_token, n_tokens, scan, n_seqs, n_kv, dk, dv, pool, \
                        status)
   if (dtype == 0) LAUNCH(float);
   if (dtype == 1) LAUNCH(__nv_bfloat16);

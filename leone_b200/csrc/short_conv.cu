@@ -257,6 +257,45 @@ __device__ __forceinline__ void min_gru_walk(const TP* __restrict__ proj, int ld
   }
 }
 
+// The same walk for four neighbouring channels of a thread (16- or 8-byte loads and stores), four rows in
+// flight.  Per channel the arithmetic and its order are those of min_gru_walk.
+constexpr int kGruVec = 4, kGruVecAhead = 4;
+
+template <typename TP, typename TO, bool kOut, bool kProduct>
+__device__ __forceinline__ void min_gru_walk4(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g_off,
+                                              const float* bz, const float* bx, int c, int first, int last, float* S,
+                                              float* A, TO* __restrict__ out, int ldo, float out_scale) {
+  for (int t0 = first; t0 < last; t0 += kGruVecAhead) {
+    float pz[kGruVecAhead][kGruVec], px[kGruVecAhead][kGruVec], pg[kGruVecAhead][kGruVec];
+#pragma unroll
+    for (int i = 0; i < kGruVecAhead; ++i) {
+      const TP* row = proj + (size_t)min(t0 + i, last - 1) * ldp + c;
+      ConvVec<TP, kGruVec>::load(row + z_off, pz[i]);
+      ConvVec<TP, kGruVec>::load(row + x_off, px[i]);
+      if (kOut) ConvVec<TP, kGruVec>::load(row + g_off, pg[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < kGruVecAhead; ++i) {
+      if (t0 + i < last) {
+        float o[kGruVec];
+#pragma unroll
+        for (int e = 0; e < kGruVec; ++e) {
+          const float z = sigmoid_f(pz[i][e] + bz[e]);
+          const float u = px[i][e] + bx[e];
+          const float cand = u >= 0.f ? u + 0.5f : sigmoid_f(u);
+          S[e] = (1.f - z) * S[e] + z * cand;
+          if (kProduct) A[e] *= 1.f - z;
+          if (kOut) {
+            const float g = pg[i][e];
+            o[e] = out_scale * S[e] * (g * sigmoid_f(g));
+          }
+        }
+        if (kOut) ConvVec<TO, kGruVec>::store(out + (size_t)(t0 + i) * ldo + c, o);
+      }
+    }
+  }
+}
+
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kConvThreads)
 min_gru_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g_off, const float* __restrict__ z_b,
@@ -283,7 +322,7 @@ min_gru_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g
 // pass 1 gives every chunk its (product of a, S at its end from a zero start); pass 2 walks a sequence's
 // chunks in order and leaves the state at each chunk's start; pass 3 walks every chunk from there and
 // writes the outputs.  The per-token arithmetic of pass 3 is that of the unchunked kernel.
-template <typename TP>
+template <typename TP, int V>
 __global__ void __launch_bounds__(kConvThreads)
 min_gru_chunk_sums_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, const float* __restrict__ z_b,
                           const float* __restrict__ x_b, const int* __restrict__ chunk_first,
@@ -291,8 +330,22 @@ min_gru_chunk_sums_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x
                           int width) {
   pdl_trigger();
   pdl_wait();
-  const int k = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
+  const int k = blockIdx.y, c = (blockIdx.x * kConvThreads + threadIdx.x) * V;
   if (c >= width) return;
+  if (V == kGruVec) {
+    float bz[kGruVec], bx[kGruVec], A[kGruVec], S[kGruVec];
+#pragma unroll
+    for (int e = 0; e < kGruVec; ++e) {
+      bz[e] = z_b != nullptr ? z_b[c + e] : 0.f;
+      bx[e] = x_b != nullptr ? x_b[c + e] : 0.f;
+      A[e] = 1.f, S[e] = 0.f;
+    }
+    min_gru_walk4<TP, float, false, true>(proj, ldp, z_off, x_off, 0, bz, bx, c, chunk_first[k], chunk_last[k], S, A,
+                                          nullptr, 0, 0.f);
+    ConvVec<float, kGruVec>::store(chunk_a + (size_t)k * width + c, A);
+    ConvVec<float, kGruVec>::store(chunk_s + (size_t)k * width + c, S);
+    return;
+  }
   const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
   float A = 1.f, S = 0.f;
   min_gru_walk<TP, float, false, true>(proj, ldp, z_off, x_off, 0, bz, bx, c, chunk_first[k], chunk_last[k], S, A,
@@ -335,7 +388,7 @@ min_gru_chunk_prefix_kernel(const int* __restrict__ seq_chunk_start, const int* 
   state[(size_t)slot * width + c] = S;
 }
 
-template <typename TP, typename TO>
+template <typename TP, typename TO, int V>
 __global__ void __launch_bounds__(kConvThreads)
 min_gru_chunk_out_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_off, int g_off,
                          const float* __restrict__ z_b, const float* __restrict__ x_b, const int* __restrict__ chunk_first,
@@ -343,8 +396,21 @@ min_gru_chunk_out_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x_
                          int ldo, int width, float out_scale) {
   pdl_trigger();
   pdl_wait();
-  const int k = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
+  const int k = blockIdx.y, c = (blockIdx.x * kConvThreads + threadIdx.x) * V;
   if (c >= width) return;
+  if (V == kGruVec) {
+    float bz[kGruVec], bx[kGruVec], A[kGruVec], S[kGruVec];
+#pragma unroll
+    for (int e = 0; e < kGruVec; ++e) {
+      bz[e] = z_b != nullptr ? z_b[c + e] : 0.f;
+      bx[e] = x_b != nullptr ? x_b[c + e] : 0.f;
+      A[e] = 1.f;
+    }
+    ConvVec<float, kGruVec>::load(chunk_s + (size_t)k * width + c, S);
+    min_gru_walk4<TP, TO, true, false>(proj, ldp, z_off, x_off, g_off, bz, bx, c, chunk_first[k], chunk_last[k], S, A,
+                                       out, ldo, out_scale);
+    return;
+  }
   const float bz = z_b != nullptr ? z_b[c] : 0.f, bx = x_b != nullptr ? x_b[c] : 0.f;
   float S = chunk_s[(size_t)k * width + c], A = 1.f;
   min_gru_walk<TP, TO, true, false>(proj, ldp, z_off, x_off, g_off, bz, bx, c, chunk_first[k], chunk_last[k], S, A, out,
@@ -443,17 +509,29 @@ extern "C" int leone_min_gru(int proj_dtype, int out_dtype, const void* proj, in
   if (n_seqs <= 0) return 0;
   if (width <= 0 || ldp < width || ldo < width || n_seqs > 65535 || n_chunks > 65535) return kRefusedSize;
   const unsigned cols = (width + kConvThreads - 1) / kConvThreads;
+  // four channels a thread in the chunk kernels where every vector starts on a 16-byte boundary
+  const bool vec = n_chunks > 0 && width % 4 == 0 && ldp % 4 == 0 && ldo % 4 == 0 && z_off % 4 == 0 && x_off % 4 == 0 &&
+                   g_off % 4 == 0 && (((uintptr_t)proj | (uintptr_t)out | (uintptr_t)chunk_a | (uintptr_t)chunk_s) & 15) == 0;
+  const unsigned vcols = (width / 4 + kConvThreads - 1) / kConvThreads;
 #define LAUNCH(TP, TO)                                                                                                  \
   {                                                                                                                     \
     if (n_chunks == 0)                                                                                                  \
       return launch_kernel(min_gru_kernel<TP, TO>, dim3(cols, n_seqs), dim3(kConvThreads), 0, stream, (const TP*)proj,  \
                            ldp, z_off, x_off, g_off, z_b, x_b, state, (TO*)out, ldo, q_start, slot_ids, width, n_slots, \
                            out_scale, status);                                                                          \
-    launch_kernel(min_gru_chunk_sums_kernel<TP>, dim3(cols, n_chunks), dim3(kConvThreads), 0, stream, (const TP*)proj,  \
-                  ldp, z_off, x_off, z_b, x_b, chunk_first, chunk_last, chunk_a, chunk_s, width);                       \
+    if (vec)                                                                                                            \
+      launch_kernel(min_gru_chunk_sums_kernel<TP, 4>, dim3(vcols, n_chunks), dim3(kConvThreads), 0, stream,             \
+                    (const TP*)proj, ldp, z_off, x_off, z_b, x_b, chunk_first, chunk_last, chunk_a, chunk_s, width);    \
+    else                                                                                                                \
+      launch_kernel(min_gru_chunk_sums_kernel<TP, 1>, dim3(cols, n_chunks), dim3(kConvThreads), 0, stream,              \
+                    (const TP*)proj, ldp, z_off, x_off, z_b, x_b, chunk_first, chunk_last, chunk_a, chunk_s, width);    \
     launch_kernel(min_gru_chunk_prefix_kernel, dim3(cols, n_seqs), dim3(kConvThreads), 0, stream, seq_chunk_start,      \
                   slot_ids, (const float*)chunk_a, chunk_s, state, width, n_slots, status);                             \
-    return launch_kernel(min_gru_chunk_out_kernel<TP, TO>, dim3(cols, n_chunks), dim3(kConvThreads), 0, stream,         \
+    if (vec)                                                                                                            \
+      return launch_kernel(min_gru_chunk_out_kernel<TP, TO, 4>, dim3(vcols, n_chunks), dim3(kConvThreads), 0, stream,   \
+                           (const TP*)proj, ldp, z_off, x_off, g_off, z_b, x_b, chunk_first, chunk_last,                \
+                           (const float*)chunk_s, (TO*)out, ldo, width, out_scale);                                     \
+    return launch_kernel(min_gru_chunk_out_kernel<TP, TO, 1>, dim3(cols, n_chunks), dim3(kConvThreads), 0, stream,      \
                          (const TP*)proj, ldp, z_off, x_off, g_off, z_b, x_b, chunk_first, chunk_last,                  \
                          (const float*)chunk_s, (TO*)out, ldo, width, out_scale);                                       \
   }

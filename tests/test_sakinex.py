@@ -405,13 +405,14 @@ def test_short_convolution_with_state_against_the_plain_sum(taps):
 
 
 @pytest.mark.gpu
-def test_min_gru_in_one_walk_and_in_chunks_against_the_plain_recurrence():
+@pytest.mark.parametrize("width", [150, 152])      # 152: the chunk kernels take four channels a thread
+def test_min_gru_in_one_walk_and_in_chunks_against_the_plain_recurrence(width):
     """Gate logits and candidates on both sides of zero; a state carried over from an earlier step; the
     walk token by token and the chunked form agree with the plain recurrence."""
     from leone_b200.ops.cuda import CudaOps
     ops = CudaOps("cuda:0", torch.float32)
     g = torch.Generator().manual_seed(4)
-    width, lens = 150, [61, 1, 18]
+    lens = [61, 1, 18]
     proj = torch.randn(sum(lens), 3 * width, generator=g) * 3.0
     zb, xb = torch.randn(width, generator=g), torch.randn(width, generator=g)
     start = torch.randn(4, width, generator=g)
@@ -435,6 +436,9 @@ def test_min_gru_in_one_walk_and_in_chunks_against_the_plain_recurrence():
         ops.min_gru(ctx, proj.cuda(), zb.cuda(), xb.cuda(), state, out, out_scale=0.7, chunk=chunk)
         assert float((out.cpu().double() - want).abs().max()) <= 2e-5 * float(want.abs().max()), chunk
         assert torch.equal(state[2].cpu(), start[2])
+        half = torch.zeros(sum(lens), width, device="cuda:0", dtype=torch.bfloat16)
+        ops.min_gru(ctx, proj.cuda(), zb.cuda(), xb.cuda(), start.clone().cuda(), half, out_scale=0.7, chunk=chunk)
+        assert float((half.cpu().double() - want).abs().max()) <= 1e-2 * float(want.abs().max()), chunk
 
 
 @pytest.mark.gpu
