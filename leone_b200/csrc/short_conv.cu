@@ -114,6 +114,18 @@ short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restric
     for (int e = 0; e < V; ++e) wt[j][e] = j < taps ? w[(size_t)(c + e) * taps + j] : 0.f;
   pdl_wait();
   const int t_end = min(t0 + kConvTile, n_tokens);
+  // Input r of the tile is row t0 - (taps - 1) + r of the step.  The rows are asked for before anything is
+  // known about the sequence (a row of the step is there to be read whichever sequence it belongs to), so
+  // that the look-ups below do not stand in front of them; a row from before the sequence's first token of
+  // this step is then replaced by its state row.
+  float v[kConvTile + kT - 1][V];
+#pragma unroll
+  for (int r = 0; r < kConvTile + kT - 1; ++r) {
+#pragma unroll
+    for (int e = 0; e < V; ++e) v[r][e] = 0.f;
+    const int row = t0 - (taps - 1) + r;
+    if (r < kConvTile + taps - 1 && row >= 0 && row < t_end) ConvVec<TI, V>::load(x + (size_t)row * ldx + c, v[r]);
+  }
   const int s0 = seq_of_token[t0], s1 = seq_of_token[t_end - 1];
   if (s0 == s1 && s0 >= 0 && s0 < n_seqs) {
     const int slot = taps > 1 ? slot_ids[s0] : 0;
@@ -122,20 +134,12 @@ short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restric
       return;
     }
     const int local0 = t0 - q_start[s0];
-    const float* st = state + (size_t)slot * (taps - 1) * channels;
-    float v[kConvTile + kT - 1][V];
-    // input r of the tile is the sequence's token local0 - (taps - 1) + r of this step, or a state row before it
+    if (local0 < taps - 1) {                             // block-uniform: the tile starts within taps - 1 of the step's start
+      const float* st = state + (size_t)slot * (taps - 1) * channels;
 #pragma unroll
-    for (int r = 0; r < kConvTile + kT - 1; ++r) {
-#pragma unroll
-      for (int e = 0; e < V; ++e) v[r][e] = 0.f;
-      if (r < kConvTile + taps - 1) {
-        const int i = local0 - (taps - 1) + r;
-        if (i >= 0) {
-          if (t0 - (taps - 1) + r < t_end) ConvVec<TI, V>::load(x + (size_t)(t0 - (taps - 1) + r) * ldx + c, v[r]);
-        } else {
-          ConvVec<float, V>::load(st + (size_t)(taps - 1 + i) * channels + c, v[r]);
-        }
+      for (int r = 0; r < kT - 1; ++r) {
+        const int i = local0 - (taps - 1) + r;           // the sequence's token i of this step; negative: state row taps - 1 + i
+        if (r < taps - 1 && i < 0) ConvVec<float, V>::load(st + (size_t)(taps - 1 + i) * channels + c, v[r]);
       }
     }
 #pragma unroll
@@ -354,38 +358,71 @@ min_gru_chunk_sums_kernel(const TP* __restrict__ proj, int ldp, int z_off, int x
   chunk_s[(size_t)k * width + c] = S;
 }
 
-__global__ void __launch_bounds__(kConvThreads)
+// Pass 2 for 32 channels of one sequence by 32 x kPrefixGroups threads: the sequence's chunks are cut
+// into kPrefixGroups runs; a thread composes its run's chunks into one (a, b), the runs' starting states
+// follow from those in shared memory, and the thread walks its run again from there.  The chain of
+// dependent steps is two runs long instead of the whole sequence.
+constexpr int kPrefixGroups = 16;
+
+__global__ void __launch_bounds__(32 * kPrefixGroups)
 min_gru_chunk_prefix_kernel(const int* __restrict__ seq_chunk_start, const int* __restrict__ slot_ids,
                             const float* __restrict__ chunk_a, float* __restrict__ chunk_s, float* __restrict__ state,
                             int width, int n_slots, int* status) {
   pdl_trigger();
   pdl_wait();
-  const int s = blockIdx.y, c = blockIdx.x * kConvThreads + threadIdx.x;
-  if (c >= width) return;
+  __shared__ float run_a[kPrefixGroups][32], run_b[kPrefixGroups][32];
+  const int s = blockIdx.y, c = blockIdx.x * 32 + threadIdx.x, gy = threadIdx.y;
   const int slot = slot_ids[s];
-  if (slot < 0 || slot >= n_slots) {
-    if (threadIdx.x == 0) set_status(status, kBadSequence, s, slot);
+  if (slot < 0 || slot >= n_slots) {                     // block-uniform
+    if (threadIdx.x == 0 && gy == 0) set_status(status, kBadSequence, s, slot);
     return;
   }
-  float S = state[(size_t)slot * width + c];
+  const bool live = c < width;
   const int k_first = seq_chunk_start[s], k_last = seq_chunk_start[s + 1];
-  for (int k0 = k_first; k0 < k_last; k0 += kGruAhead) {
+  const int per = (k_last - k_first + kPrefixGroups - 1) / kPrefixGroups;
+  const int k0 = min(k_first + gy * per, k_last), k1 = min(k0 + per, k_last);
+  float A = 1.f, B = 0.f;
+  if (live) {
+    for (int kk = k0; kk < k1; kk += kGruAhead) {
+      float a[kGruAhead], b[kGruAhead];
+#pragma unroll
+      for (int i = 0; i < kGruAhead; ++i) {
+        const int k = min(kk + i, k1 - 1);
+        a[i] = chunk_a[(size_t)k * width + c];
+        b[i] = chunk_s[(size_t)k * width + c];
+      }
+#pragma unroll
+      for (int i = 0; i < kGruAhead; ++i) {
+        if (kk + i < k1) {
+          B = a[i] * B + b[i];
+          A *= a[i];
+        }
+      }
+    }
+  }
+  run_a[gy][threadIdx.x] = A;
+  run_b[gy][threadIdx.x] = B;
+  __syncthreads();
+  if (!live) return;
+  float S = state[(size_t)slot * width + c];
+  for (int g = 0; g < gy; ++g) S = run_a[g][threadIdx.x] * S + run_b[g][threadIdx.x];
+  if (gy == kPrefixGroups - 1) state[(size_t)slot * width + c] = A * S + B;      // the state after the step
+  for (int kk = k0; kk < k1; kk += kGruAhead) {
     float a[kGruAhead], b[kGruAhead];
 #pragma unroll
     for (int i = 0; i < kGruAhead; ++i) {
-      const int k = min(k0 + i, k_last - 1);
+      const int k = min(kk + i, k1 - 1);
       a[i] = chunk_a[(size_t)k * width + c];
       b[i] = chunk_s[(size_t)k * width + c];
     }
 #pragma unroll
     for (int i = 0; i < kGruAhead; ++i) {
-      if (k0 + i < k_last) {
-        chunk_s[(size_t)(k0 + i) * width + c] = S;       // from here on: the state at the chunk's start
+      if (kk + i < k1) {
+        chunk_s[(size_t)(kk + i) * width + c] = S;         // from here on: the state at the chunk's start
         S = a[i] * S + b[i];
       }
     }
   }
-  state[(size_t)slot * width + c] = S;
 }
 
 template <typename TP, typename TO, int V>
@@ -525,8 +562,8 @@ extern "C" int leone_min_gru(int proj_dtype, int out_dtype, const void* proj, in
     else                                                                                                                \
       launch_kernel(min_gru_chunk_sums_kernel<TP, 1>, dim3(cols, n_chunks), dim3(kConvThreads), 0, stream,              \
                     (const TP*)proj, ldp, z_off, x_off, z_b, x_b, chunk_first, chunk_last, chunk_a, chunk_s, width);    \
-    launch_kernel(min_gru_chunk_prefix_kernel, dim3(cols, n_seqs), dim3(kConvThreads), 0, stream, seq_chunk_start,      \
-                  slot_ids, (const float*)chunk_a, chunk_s, state, width, n_slots, status);                             \
+    launch_kernel(min_gru_chunk_prefix_kernel, dim3((width + 31) / 32, n_seqs), dim3(32, kPrefixGroups), 0, stream,     \
+                  seq_chunk_start, slot_ids, (const float*)chunk_a, chunk_s, state, width, n_slots, status);            \
     if (vec)                                                                                                            \
       return launch_kernel(min_gru_chunk_out_kernel<TP, TO, 4>, dim3(vcols, n_chunks), dim3(kConvThreads), 0, stream,   \
                            (const TP*)proj, ldp, z_off, x_off, g_off, z_b, x_b, chunk_first, chunk_last,                \

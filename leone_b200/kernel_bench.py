@@ -237,7 +237,7 @@ def bench_masked_attention(ops, tokens, batch, context, n_q, n_kv, dk, dv, mask,
     cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=page_tokens)
     bias = torch.zeros(n_q, device=DEV) if weights == "sigmoid" else None
     ms = _time(lambda: ops.attention_masked(ctx, qkv, out, n_q, n_kv, dk, dv, dk ** -0.5, mask, size, weights, bias, cache),
-               reps, warmup)
+               reps, warmup, per_graph=16 if decode else 1)     # a decode step's kernel takes microseconds
     # keys a query at position p sees
     def seen(p):
         return p + 1 if mask == "causal" else (min(p + 1, size) if mask == "window" else p % size + 1)
@@ -296,7 +296,11 @@ def bench_pooled_attention(ops, tokens, batch, context, n_q, n_kv, dk, dv, windo
     def seen(p):
         return min(p + 1, window) + max(p - window + 1, 0) // pool
     members = seqs * seen(length - 1) if decode else sum(seen(p) for p in range(tokens))
-    ms = _time(lambda: ops.attention_pooled(ctx, q, out, tok, blk, n_q, n_kv, dk, dv, dk ** -0.5, window, pool), reps, warmup)
+    # the kernels of a decode step and the block means take microseconds: several launches (on the same
+    # operands) in one graph, so that the time is the kernels' and not the graph launch's
+    small = 16 if decode else 4
+    ms = _time(lambda: ops.attention_pooled(ctx, q, out, tok, blk, n_q, n_kv, dk, dv, dk ** -0.5, window, pool), reps, warmup,
+               per_graph=small if decode else 1)
     row = dict(kernel="attention_pooled", window=window, pool=pool, dk=dk, dv=dv, us=ms * 1e3)
     if decode:
         row.update(batch=batch, context=context, gbs=members * n_kv * (dk + dv) * 2.0 / ms / 1e6)
@@ -304,10 +308,10 @@ def bench_pooled_attention(ops, tokens, batch, context, n_q, n_kv, dk, dv, windo
         row.update(tokens=tokens, tflops=2.0 * n_q * (dk + dv) * members / ms / 1e9)
     result.append(row)
     ms = _time(lambda: ops.attention_pooled_prepare(ctx, proj, q, n_q, n_kv, dk, dv, conv_w, state, freqs, "half_split",
-                                                    1.0, True, 1e-6, tok), reps, warmup)
+                                                    1.0, True, 1e-6, tok), reps, warmup, per_graph=small)
     moved = n * (cols * 4 * (2 if decode and taps > 1 else 1) + cols * 2)        # rows read (state rows too in a decode step), q and pages written
     result.append(dict(kernel="attention_pooled_prepare", tokens=n, cols=cols, taps=taps, us=ms * 1e3, gbs=moved / ms / 1e6))
-    ms = _time(lambda: ops.attention_pool_blocks(ctx, tok, blk, n_kv, dk, dv, pool), reps, warmup)
+    ms = _time(lambda: ops.attention_pool_blocks(ctx, tok, blk, n_kv, dk, dv, pool), reps, warmup, per_graph=small)
     ended = seqs * (1 if decode and length % pool == 0 else 0) if decode else tokens // pool
     moved = ended * n_kv * (dk + dv) * 2 * (pool + 1)
     result.append(dict(kernel="attention_pool_blocks", tokens=n, blocks=ended, us=ms * 1e3, gbs=moved / ms / 1e6))
