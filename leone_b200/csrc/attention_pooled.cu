@@ -30,6 +30,7 @@
 namespace leone {
 
 constexpr int kPoolPrepThreads = 256;
+constexpr int kPrepTaps = 4, kPrepCols = 4;      // the convolution's unrolled form: taps it takes, columns a thread has in flight
 
 template <typename TP, typename T>
 __global__ void __launch_bounds__(kPoolPrepThreads)
@@ -51,6 +52,16 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
   float* head_f = buf + cols;           // [heads] the heads' norm factors
   float* cs = head_f + heads;           // [rot_dims] cos, sin per pair (times the magnitude)
   const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, warps = kPoolPrepThreads / 32;
+  // A token's heads do not depend on one another: gridDim.y blocks share them (a step of few tokens has
+  // few blocks otherwise).  The units are the q heads, the k heads and the v heads in the order of the
+  // row's columns; this block takes units u_lo .. u_hi - 1, that is columns c_lo .. c_hi - 1 and, of the
+  // heads that are rotated and normed, h_lo .. h_hi - 1.
+  const int units = heads + n_kv, per = (units + gridDim.y - 1) / gridDim.y;
+  const int u_lo = blockIdx.y * per, u_hi = min(units, u_lo + per);
+  if (u_lo >= units) return;
+  const int c_lo = u_lo <= heads ? u_lo * dk : qk + (u_lo - heads) * dv;
+  const int c_hi = u_hi <= heads ? u_hi * dk : qk + (u_hi - heads) * dv;
+  const int h_lo = min(u_lo, heads), h_hi = min(u_hi, heads);
   const int pos = positions[t], s = seq_of_token[t];
   if (pos < 0 || s < 0 || s >= n_seqs) {
     if (tid == 0) set_status(status, pos < 0 ? kBadPosition : kBadSequence, t, pos < 0 ? pos : s);
@@ -65,23 +76,56 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
     }
     const int local = t - q_start[s];
     const float* st = conv_state + (size_t)slot * (taps - 1) * cols;
-    for (int c = tid; c < cols; c += kPoolPrepThreads) {
-      float acc = 0.f;
-      for (int j = 0; j < taps; ++j) {
-        const int back = taps - 1 - j;
-        const float v = back <= local ? to_float<TP>(proj[(size_t)(t - back) * ldp + c])
+    if (taps <= kPrepTaps) {
+      // up to four taps: the inputs and weights of four columns a thread are asked for together, then the
+      // sums are formed (in ascending j, as below)
+      for (int c0 = c_lo + tid; c0 < c_hi; c0 += kPoolPrepThreads * kPrepCols) {
+        float v[kPrepCols][kPrepTaps], w[kPrepCols][kPrepTaps];
+#pragma unroll
+        for (int u = 0; u < kPrepCols; ++u) {
+          const int c = min(c0 + u * kPoolPrepThreads, c_hi - 1);
+#pragma unroll
+          for (int j = 0; j < kPrepTaps; ++j) {
+            v[u][j] = 0.f, w[u][j] = 0.f;
+            if (j < taps) {
+              const int back = taps - 1 - j;
+              v[u][j] = back <= local ? to_float<TP>(proj[(size_t)(t - back) * ldp + c])
                                       : st[(size_t)(taps - 1 + local - back) * cols + c];
-        acc = fmaf(conv_w[(size_t)c * taps + j], v, acc);
+              w[u][j] = conv_w[(size_t)c * taps + j];
+            }
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kPrepCols; ++u) {
+          const int c = c0 + u * kPoolPrepThreads;
+          if (c < c_hi) {
+            float acc = 0.f;
+#pragma unroll
+            for (int j = 0; j < kPrepTaps; ++j)
+              if (j < taps) acc = fmaf(w[u][j], v[u][j], acc);
+            buf[c] = acc;
+          }
+        }
       }
-      buf[c] = acc;
+    } else {
+      for (int c = c_lo + tid; c < c_hi; c += kPoolPrepThreads) {
+        float acc = 0.f;
+        for (int j = 0; j < taps; ++j) {
+          const int back = taps - 1 - j;
+          const float v = back <= local ? to_float<TP>(proj[(size_t)(t - back) * ldp + c])
+                                        : st[(size_t)(taps - 1 + local - back) * cols + c];
+          acc = fmaf(conv_w[(size_t)c * taps + j], v, acc);
+        }
+        buf[c] = acc;
+      }
     }
   } else if (taps == 1) {
-    for (int c = tid; c < cols; c += kPoolPrepThreads) buf[c] = conv_w[c] * to_float<TP>(row[c]);
+    for (int c = c_lo + tid; c < c_hi; c += kPoolPrepThreads) buf[c] = conv_w[c] * to_float<TP>(row[c]);
   } else {
-    for (int c = tid; c < cols; c += kPoolPrepThreads) buf[c] = to_float<TP>(row[c]);
+    for (int c = c_lo + tid; c < c_hi; c += kPoolPrepThreads) buf[c] = to_float<TP>(row[c]);
   }
   const int half = rot_dims >> 1;
-  for (int i = tid; i < half; i += kPoolPrepThreads) {
+  for (int i = tid; i < (h_lo < h_hi ? half : 0); i += kPoolPrepThreads) {
     const float angle = (float)pos * freqs[i];
     float sn, co;
     sincosf(angle, &sn, &co);
@@ -90,7 +134,7 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
   }
   __syncthreads();
   // rotation: every thread forms both members of its pairs, so nothing is read after it was written
-  for (int i = tid; i < heads * half; i += kPoolPrepThreads) {
+  for (int i = h_lo * half + tid; i < h_hi * half; i += kPoolPrepThreads) {
     const int h = i / half, pair = i - h * half;
     const int ia = h * dk + (adjacent ? 2 * pair : pair), ib = h * dk + (adjacent ? 2 * pair + 1 : pair + half);
     const float a = buf[ia], b = buf[ib], co = cs[2 * pair], sn = cs[2 * pair + 1];
@@ -98,7 +142,7 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
     buf[ib] = b * co + a * sn;
   }
   __syncthreads();
-  for (int h = warp; h < heads; h += warps) {
+  for (int h = h_lo + warp; h < h_hi; h += warps) {
     float f = 1.f;
     if (unit_norm) {
       float ss = 0.f;
@@ -121,14 +165,14 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
     key_at = at * dk;
     value_at = at * dv;
   }
-  for (int c = tid; c < qk; c += kPoolPrepThreads) {
+  for (int c = c_lo + tid; c < min(c_hi, qk); c += kPoolPrepThreads) {
     const int h = c / dk, e = c - h * dk;
     const T o = from_float<T>(buf[c] * head_f[h]);
     if (h < n_q) q_out[(size_t)t * ldq + c] = o;
     else if (key_at >= 0) k_pool[key_at + (long long)(h - n_q) * page_tokens * dk + e] = o;
   }
   if (value_at >= 0) {
-    for (int c = tid; c < n_kv * dv; c += kPoolPrepThreads) {
+    for (int c = max(c_lo, qk) - qk + tid; c < max(c_hi, qk) - qk; c += kPoolPrepThreads) {
       const int h = c / dv, e = c - h * dv;
       v_pool[value_at + (long long)h * page_tokens * dv + e] = from_float<T>(buf[qk + c]);
     }
@@ -370,12 +414,15 @@ extern "C" int leone_attention_pooled_prepare(int proj_dtype, int dtype, const v
   if (ldp < cols || ldq < n_q * dk) return kRefusedSize;
   const size_t smem = ((size_t)cols + (n_q + n_kv) + rot_dims + 2) * sizeof(float);
   if (smem > 200 * 1024) return kRefusedSize;
+  // a step of few tokens: the heads of a token are shared out over blocks until the SMs have two blocks each
+  const int units = n_q + 2 * n_kv;
+  const int parts = n_tokens >= 296 ? 1 : min(units, max(1, 296 / n_tokens));
 #define LAUNCH(TP, T)                                                                                                 \
   {                                                                                                                   \
     if (smem > 48 * 1024)                                                                                             \
       cudaFuncSetAttribute(attention_pooled_prepare_kernel<TP, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                            (int)smem);                                                                                \
-    return launch_kernel(attention_pooled_prepare_kernel<TP, T>, dim3(n_tokens), dim3(kPoolPrepThreads), smem, stream, \
+    return launch_kernel(attention_pooled_prepare_kernel<TP, T>, dim3(n_tokens, parts), dim3(kPoolPrepThreads), smem, stream, \
                          (const TP*)proj, ldp, n_q, n_kv, dk, dv, conv_w, taps, conv_state, freqs, rot_dims, adjacent, \
                          magnitude, unit_norm, eps, (T*)q_out, ldq, positions, seq_of_token, q_start, slot_ids,       \
                          n_slots, block_table, table_width, n_seqs, (T*)k_pool, (T*)v_pool, num_pages, page_tokens,   \
