@@ -35,7 +35,7 @@ constexpr int kPrepTaps = 4, kPrepCols = 4;      // the convolution's unrolled f
 template <typename TP, typename T>
 __global__ void __launch_bounds__(kPoolPrepThreads)
 attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, int n_kv, int dk, int dv,
-                                const float* __restrict__ conv_w, int taps, const float* __restrict__ conv_state,
+                                const float* __restrict__ conv_w, int taps, float* conv_state, int update_state,
                                 const float* __restrict__ freqs, int rot_dims, int adjacent, float magnitude,
                                 int unit_norm, float eps, T* __restrict__ q_out, int ldq,
                                 const int* __restrict__ positions, const int* __restrict__ seq_of_token,
@@ -75,7 +75,9 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
       return;
     }
     const int local = t - q_start[s];
-    const float* st = conv_state + (size_t)slot * (taps - 1) * cols;
+    float* st = conv_state + (size_t)slot * (taps - 1) * cols;
+    // a step in which every sequence brings one token: the thread that reads a state column also moves it on
+    const bool move_on = update_state && local == 0 && q_start[s + 1] - q_start[s] == 1;
     if (taps <= kPrepTaps) {
       // up to four taps: the inputs and weights of four columns a thread are asked for together, then the
       // sums are formed (in ascending j, as below)
@@ -104,6 +106,11 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
             for (int j = 0; j < kPrepTaps; ++j)
               if (j < taps) acc = fmaf(w[u][j], v[u][j], acc);
             buf[c] = acc;
+            if (move_on) {                               // v[u][1 .. taps - 1]: the state's rows 1 .. and the token's own input
+#pragma unroll
+              for (int j = 1; j < kPrepTaps; ++j)
+                if (j < taps) st[(size_t)(j - 1) * cols + c] = v[u][j];
+            }
           }
         }
       }
@@ -117,6 +124,10 @@ attention_pooled_prepare_kernel(const TP* __restrict__ proj, int ldp, int n_q, i
           acc = fmaf(conv_w[(size_t)c * taps + j], v, acc);
         }
         buf[c] = acc;
+        if (move_on) {
+          for (int r = 0; r + 2 < taps; ++r) st[(size_t)r * cols + c] = st[(size_t)(r + 1) * cols + c];
+          st[(size_t)(taps - 2) * cols + c] = to_float<TP>(row[c]);
+        }
       }
     }
   } else if (taps == 1) {
@@ -397,7 +408,7 @@ using namespace leone;
 // convolution.  freqs null: no rotation.  k_pool null: nothing is written into pages.
 extern "C" int leone_attention_pooled_prepare(int proj_dtype, int dtype, const void* proj, int ldp, int n_tokens, int n_q,
                                               int n_kv, int dk, int dv, const float* conv_w, int taps,
-                                              const float* conv_state, const float* freqs, int rot_dims, int adjacent,
+                                              float* conv_state, int update_state, const float* freqs, int rot_dims, int adjacent,
                                               float magnitude, int unit_norm, float eps, void* q_out, int ldq,
                                               const int* positions, const int* seq_of_token, const int* q_start,
                                               const int* slot_ids, int n_slots, const int* block_table, int table_width,
@@ -423,7 +434,7 @@ extern "C" int leone_attention_pooled_prepare(int proj_dtype, int dtype, const v
       cudaFuncSetAttribute(attention_pooled_prepare_kernel<TP, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,       \
                            (int)smem);                                                                                \
     return launch_kernel(attention_pooled_prepare_kernel<TP, T>, dim3(n_tokens, parts), dim3(kPoolPrepThreads), smem, stream, \
-                         (const TP*)proj, ldp, n_q, n_kv, dk, dv, conv_w, taps, conv_state, freqs, rot_dims, adjacent, \
+                         (const TP*)proj, ldp, n_q, n_kv, dk, dv, conv_w, taps, conv_state, update_state, freqs, rot_dims, adjacent, \
                          magnitude, unit_norm, eps, (T*)q_out, ldq, positions, seq_of_token, q_start, slot_ids,       \
                          n_slots, block_table, table_width, n_seqs, (T*)k_pool, (T*)v_pool, num_pages, page_tokens,   \
                          status);                                                                                     \

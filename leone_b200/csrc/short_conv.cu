@@ -15,7 +15,9 @@
 // The state is [slots, taps - 1, channels] fp32, row taps - 2 the newest input.  Weights are fp32
 // [channels, taps].  All sums are fp32 in ascending j, so a token's result does not depend on how
 // its sequence was cut into steps.  The convolution does not write the state (tokens at a step's
-// start still read it); the state kernel runs after it.
+// start still read it); the state kernel runs after it.  In a step where every sequence brings one
+// token (update_state) the convolution's thread of (token, channel) is the only reader and writer of
+// its state column and moves it on itself.
 #include "common.cuh"
 
 namespace leone {
@@ -25,10 +27,10 @@ constexpr int kMaxTaps = 16;
 
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(kConvThreads)
-short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w, const float* __restrict__ state,
+short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w, float* state,
                   TO* __restrict__ out, int ldo, const int* __restrict__ q_start, const int* __restrict__ seq_of_token,
-                  const int* __restrict__ slot_ids, int channels, int taps, int add_input, int n_seqs, int n_slots,
-                  int* status) {
+                  const int* __restrict__ slot_ids, int channels, int taps, int add_input, int update_state, int n_seqs,
+                  int n_slots, int* status) {
   pdl_trigger();
   pdl_wait();
   const int t = blockIdx.x, c = blockIdx.y * kConvThreads + threadIdx.x;
@@ -44,7 +46,7 @@ short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w
     return;
   }
   const int local = t - q_start[s];                 // tokens of the sequence in this step before this one
-  const float* st = state + (size_t)slot * (taps - 1) * channels;
+  float* st = state + (size_t)slot * (taps - 1) * channels;
   float acc = 0.f;
   for (int j = 0; j < taps; ++j) {
     const int back = taps - 1 - j;
@@ -55,6 +57,10 @@ short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w
   }
   if (add_input) acc += to_float<TI>(x[(size_t)t * ldx + c]);
   out[(size_t)t * ldo + c] = from_float<TO>(acc);
+  if (update_state && taps > 1 && local == 0 && q_start[s + 1] - q_start[s] == 1) {
+    for (int r = 0; r + 2 < taps; ++r) st[(size_t)r * channels + c] = st[(size_t)(r + 1) * channels + c];
+    st[(size_t)(taps - 2) * channels + c] = to_float<TI>(x[(size_t)t * ldx + c]);
+  }
 }
 
 // The same for kConvTile consecutive tokens of V neighbouring channels per thread (steps of many
@@ -485,15 +491,16 @@ extern "C" int leone_add_scaled(float* x, const float* y, long long n, float sca
 }
 
 // in_dtype / out_dtype: 0 float32, 1 bfloat16.
-extern "C" int leone_short_conv(int in_dtype, int out_dtype, const void* x, int ldx, const float* w, const float* state,
+// update_state: every sequence of the step brings one token, and the kernel moves the state on too.
+extern "C" int leone_short_conv(int in_dtype, int out_dtype, const void* x, int ldx, const float* w, float* state,
                                 void* out, int ldo, const int* q_start, const int* seq_of_token, const int* slot_ids,
-                                int n_tokens, int channels, int taps, int add_input, int n_seqs, int n_slots,
-                                int* status, cudaStream_t stream) {
+                                int n_tokens, int channels, int taps, int add_input, int update_state, int n_seqs,
+                                int n_slots, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (channels <= 0 || taps < 1 || taps > kMaxTaps || ldx < channels || ldo < channels) return kRefusedSize;
   if (taps > 1 && state == nullptr) return kRefusedSize;
   const dim3 grid(n_tokens, (channels + kConvThreads - 1) / kConvThreads);
-  const bool tiled = n_tokens >= 16 * kConvTile;        // a decode step's tokens each belong to another sequence
+  const bool tiled = n_tokens >= 16 * kConvTile && !update_state;      // a decode step's tokens each belong to another sequence
   // four channels a thread where every row starts on a 16-byte boundary and the taps fit the small form
   const bool vec = tiled && taps <= 4 && channels % 4 == 0 && ldx % 4 == 0 && ldo % 4 == 0 &&
                    (((uintptr_t)x | (uintptr_t)out | (uintptr_t)state) & 15) == 0;
@@ -510,8 +517,8 @@ extern "C" int leone_short_conv(int in_dtype, int out_dtype, const void* x, int 
                            (const TI*)x, ldx, w, state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, n_tokens,  \
                            channels, taps, add_input, n_seqs, n_slots, status);                                     \
     return launch_kernel(short_conv_kernel<TI, TO>, grid, dim3(kConvThreads), 0, stream, (const TI*)x, ldx, w,      \
-                         state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, channels, taps, add_input, n_seqs,  \
-                         n_slots, status);                                                                          \
+                         state, (TO*)out, ldo, q_start, seq_of_token, slot_ids, channels, taps, add_input,          \
+                         update_state, n_seqs, n_slots, status);                                                    \
   }
   if (in_dtype == 0 && out_dtype == 0) LAUNCH(float, float);
   if (in_dtype == 0 && out_dtype == 1) LAUNCH(float, __nv_bfloat16);

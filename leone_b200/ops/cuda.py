@@ -646,10 +646,13 @@ class CudaOps:
         return logits
 
     # -- short convolutions with state, the minGRU recurrence, pooled-window attention --------------
-    def short_conv(self, ctx, x, weight, state, out, add_input=False):
+    def short_conv(self, ctx, x, weight, state, out, add_input=False, update_state=False):
         """``out_t = (x_t if add_input) + sum_j weight[:, j] x_(t - taps + 1 + j)`` on every channel,
         inputs before the step from ``state`` (fp32 ``[slots, taps - 1, channels]``), which is not
-        changed (``csrc/short_conv.cu``).  ``weight``: fp32 ``[channels, taps]``."""
+        changed (``csrc/short_conv.cu``) unless ``update_state``, which is for steps in which every
+        sequence brings one token: the kernel then leaves the state as :meth:`short_conv_state`
+        would.  ``weight``: fp32 ``[channels, taps]``."""
+        _need(not update_state or ctx.decode_only, "short_conv: update_state is for steps of one token a sequence")
         n, channels = out.shape
         taps = weight.shape[1]
         _need(x.shape == (n, channels) and x.stride(1) == 1 and out.stride(1) == 1 and weight.dtype == torch.float32
@@ -660,7 +663,8 @@ class CudaOps:
         _check(self.mixers.leone_short_conv(
             _dt(x.dtype), _dt(out.dtype), _ptr(x), x.stride(0), _ptr(weight), _ptr(state), _ptr(out), out.stride(0),
             _ptr(ctx.q_start), _ptr(ctx.seq_of_token), _ptr(ctx.slot_ids), n, channels, taps, 1 if add_input else 0,
-            ctx.n_seqs, state.shape[0] if state is not None else 0, _ptr(ctx.status), self._stream()), "short_conv")
+            1 if update_state else 0, ctx.n_seqs, state.shape[0] if state is not None else 0, _ptr(ctx.status),
+            self._stream()), "short_conv")
 
     def short_conv_state(self, ctx, x, state):
         """The state after the step: the last ``taps - 1`` rows of ``x`` of every sequence (older
@@ -724,7 +728,7 @@ class CudaOps:
                                             self._stream()), "add_scaled")
 
     def attention_pooled_prepare(self, ctx, proj, q_out, n_q, n_kv, dk, dv, conv_w, conv_state, freqs, pairing,
-                                 magnitude, unit_norm, eps, cache):
+                                 magnitude, unit_norm, eps, cache, update_state=False):
         """Per token, in fp32: the short convolution of the projected row ``[q | k | v]`` (weights
         fp32 ``[cols, taps]`` or None; earlier inputs from ``conv_state``), the rotation of q and k,
         the unit RMS norm of every q and k head, q into ``q_out``, k and v into their pages
@@ -753,7 +757,7 @@ class CudaOps:
         self.launches += 1
         _check(self.mixers.leone_attention_pooled_prepare(
             _dt(proj.dtype), _dt(q_out.dtype), _ptr(proj), proj.stride(0), n, n_q, n_kv, dk, dv, _ptr(conv_w), taps,
-            _ptr(conv_state), _ptr(freqs), rot, 1 if pairing == "adjacent" else 0, c_float(magnitude),
+            _ptr(conv_state), 1 if (update_state and ctx.decode_only) else 0, _ptr(freqs), rot, 1 if pairing == "adjacent" else 0, c_float(magnitude),
             1 if unit_norm else 0, c_float(eps), _ptr(q_out), q_out.stride(0), _ptr(ctx.positions),
             _ptr(ctx.seq_of_token), _ptr(ctx.q_start), _ptr(ctx.slot_ids),
             conv_state.shape[0] if conv_state is not None else 0, _ptr(bt), bt.shape[1], bt.shape[0],

@@ -100,9 +100,11 @@ class PooledWindowAttention(Mixer):
         if self.pos is not None:
             freqs, pairing, magnitude = self.pos.frequencies(), self.pos.pairing, float(getattr(self.pos, "magnitude", 1.0))
         state = conv.state if conv is not None else None
+        # a step of one token a sequence: the preparation kernel moves the convolution's state on itself
+        fused = state is not None and conv.writes and bool(ctx.decode_only)
         ops.attention_pooled_prepare(ctx, proj, q, self.n_q, self.n_kv, self.d, self.dv, self.conv_w, state, freqs,
-                                     pairing, magnitude, self.unit_norm, self.eps, tokens)
-        if state is not None and conv.writes:
+                                     pairing, magnitude, self.unit_norm, self.eps, tokens, update_state=fused)
+        if state is not None and conv.writes and not fused:
             ops.short_conv_state(ctx, proj, state)
         if tokens.writes:
             ops.attention_pool_blocks(ctx, tokens, blocks, self.n_kv, self.d, self.dv, self.pool)

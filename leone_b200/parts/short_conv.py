@@ -47,7 +47,9 @@ class ShortConv(Part):
         rt, ops = self.rt, self.rt.ops
         out = rt.buffer(out_name, x.shape[0], self.channels, out_dtype or rt.dtype)
         state = cache.state if cache is not None else None
-        ops.short_conv(ctx, x, self.weight, state, out, add_input=self.add_input)
-        if state is not None and cache.writes:
+        # a step of one token a sequence: the convolution's kernel moves the state on itself
+        fused = state is not None and cache.writes and bool(ctx.decode_only)
+        ops.short_conv(ctx, x, self.weight, state, out, add_input=self.add_input, update_state=fused)
+        if state is not None and cache.writes and not fused:
             ops.short_conv_state(ctx, x, state)
         return out

@@ -310,8 +310,10 @@ class EmulatedOps:
                 out[a + t] = (weight.t() * hist[t:t + taps]).sum(dim=0)
         return out + x if add_input else out
 
-    def short_conv(self, ctx, x, weight, state, out, add_input=False):
+    def short_conv(self, ctx, x, weight, state, out, add_input=False, update_state=False):
         out.copy_(self._conv_rows(ctx, x, weight, state, add_input).to(out.dtype))
+        if update_state and state is not None:
+            self.short_conv_state(ctx, x, state)
 
     def short_conv_state(self, ctx, x, state):
         keep, channels = state.shape[1], state.shape[2]
@@ -343,9 +345,11 @@ class EmulatedOps:
         x.add_(y, alpha=scale)
 
     def attention_pooled_prepare(self, ctx, proj, q_out, n_q, n_kv, dk, dv, conv_w, conv_state, freqs, pairing,
-                                 magnitude, unit_norm, eps, cache):
+                                 magnitude, unit_norm, eps, cache, update_state=False):
         n = proj.shape[0]
         x = proj.float() if conv_w is None else self._conv_rows(ctx, proj, conv_w, conv_state, False)
+        if update_state and conv_state is not None:
+            self.short_conv_state(ctx, proj, conv_state)
         q, k = x[:, :n_q * dk].reshape(n, n_q, dk), x[:, n_q * dk:(n_q + n_kv) * dk].reshape(n, n_kv, dk)
         v = x[:, (n_q + n_kv) * dk:].reshape(n, n_kv, dv)
         pos = ctx.positions.long()

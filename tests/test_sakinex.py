@@ -389,8 +389,10 @@ def test_short_convolution_with_state_against_the_plain_sum(taps):
                 ctx, starts = _step_ctx([cut[s] for s in seqs], [done[s] + cut[s] for s in seqs], [(2, 0)[s] for s in seqs])
                 x = torch.cat([xs[s][done[s]:done[s] + cut[s]] for s in seqs]).to(dtype).cuda()
                 out = torch.zeros_like(x)
-                ops.short_conv(ctx, x, w.cuda(), state if taps > 1 else None, out, add_input=add_input)
-                if taps > 1:
+                # a step of single tokens: the convolution's kernel moves the state on itself
+                fused = taps > 1 and bool(ctx.decode_only)
+                ops.short_conv(ctx, x, w.cuda(), state if taps > 1 else None, out, add_input=add_input, update_state=fused)
+                if taps > 1 and not fused:
                     ops.short_conv_state(ctx, x, state)
                 assert int(ctx.status[0]) == 0
                 for i, s in enumerate(seqs):
@@ -553,12 +555,15 @@ def test_preparation_and_block_means_against_the_plain_steps():
                             table, page, True, pool)
     state = torch.zeros(2, taps - 1, cols, device="cuda:0")
     q_got = []
-    for a, b in ((0, 28), (28, 29), (29, 45)):
+    for a, b in ((0, 28), (28, 29), (29, 30), (30, 45)):     # the steps of one token move the state on in the kernel
         ctx, _ = _step_ctx([b - a], [b], [1])
         q_out = torch.zeros(b - a, n_q * dk, device="cuda:0")
+        fused = bool(ctx.decode_only)
         ops.attention_pooled_prepare(ctx, proj[a:b].cuda(), q_out, n_q, n_kv, dk, dv, conv_w.cuda(), state,
-                                     pe._freqs_host.cuda(), "half_split", float(pe.magnitude), True, eps, tokens)
-        ops.short_conv_state(ctx, proj[a:b].cuda(), state)
+                                     pe._freqs_host.cuda(), "half_split", float(pe.magnitude), True, eps, tokens,
+                                     update_state=fused)
+        if not fused:
+            ops.short_conv_state(ctx, proj[a:b].cuda(), state)
         ops.attention_pool_blocks(ctx, tokens, blocks, n_kv, dk, dv, pool)
         assert int(ctx.status[0]) == 0
         q_got.append(q_out.cpu())
