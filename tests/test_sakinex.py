@@ -531,6 +531,39 @@ def test_pooled_window_attention_kernels_against_the_plain_rule(n_q, n_kv, dk, d
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("q_lens,ctx_lens,pool,page", [
+    ([600, 5, 230], [700, 77, 230], 7, 16), ([4200, 300], [4300, 900], 24, 16), ([1, 1, 1], [64, 63, 130], 32, 32)])
+def test_block_means_of_long_steps(q_lens, ctx_lens, pool, page):
+    """The kernel that forms the block means looks through 1, 8 or 32 tokens a thread block, by the
+    step's length: every block that one of the step's tokens ends gets its means, the others stay as
+    they were, whatever the grouping."""
+    from leone_b200.ops.cuda import CudaOps
+    n_kv, dk, dv = 2, 24, 40
+    for dtype, tol in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
+        ops = CudaOps("cuda:0", dtype)
+        g = torch.Generator().manual_seed(pool)
+        tokens, blocks, keys, vals = _paged_sequences(ctx_lens, n_kv, dk, dv, page, pool, dtype, g)
+        want_k, want_v = blocks.k_pool.clone(), blocks.v_pool.clone()
+        # the blocks that this step's tokens end are wiped, the others keep a mark
+        table = tokens.block_table.cpu()
+        for s, (x, c) in enumerate(zip(q_lens, ctx_lens)):
+            for b in range(c // pool):
+                e = b * pool + pool - 1
+                pg, row = int(table[s, e // page]), (e % page) // pool
+                if e >= c - x:
+                    blocks.k_pool[pg, :, row] = 0
+                    blocks.v_pool[pg, :, row] = 0
+                else:
+                    blocks.k_pool[pg, :, row] = 5.0
+                    want_k[pg, :, row] = 5.0
+        ctx, _ = _step_ctx(q_lens, ctx_lens, [0, 1, 2][:len(q_lens)])
+        ops.attention_pool_blocks(ctx, tokens, blocks, n_kv, dk, dv, pool)
+        assert int(ctx.status[0]) == 0
+        assert float((blocks.k_pool.float() - want_k.float()).abs().max()) <= tol * 4
+        assert float((blocks.v_pool.float() - want_v.float()).abs().max()) <= tol * 4
+
+
+@pytest.mark.gpu
 def test_preparation_and_block_means_against_the_plain_steps():
     """The preparation kernel (convolution with state, partial rotation with YaRN frequencies and their
     magnitude, unit norm per head, cache write) and the kernel that forms the block means, over two
