@@ -34,9 +34,11 @@ MODULES: Dict[str, List[str]] = {
     # mixers and feed-forwards beyond softmax attention over K/V pages and the dense gated layer:
     # linear attention with a decaying state, attention through a cached latent, attention with a choice
     # of mask and weight rule, routed experts, short convolutions with state, the minGRU recurrence, attention
-    # over a window of tokens and pooled blocks before it
+    # over a window of tokens and pooled blocks before it, attention whose scores are mixed across heads, the gated
+    # delta rule
     "mixers": ["linear_attention.cu", "attention_latent.cu", "attention_latent_mma.cu", "attention_masked.cu",
-               "attention_masked_mma.cu", "experts.cu", "norm_act.cu", "short_conv.cu", "attention_pooled.cu"],
+               "attention_masked_mma.cu", "experts.cu", "norm_act.cu", "short_conv.cu", "attention_pooled.cu",
+               "attention_mixed_heads.cu", "gated_delta.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
     "static": ["attention_decode_static.cu"],
     # the host side of the runtime (pages, block tables, step metadata, the scheduler's decisions,

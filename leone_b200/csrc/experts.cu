@@ -23,7 +23,8 @@ __device__ __forceinline__ float silu_e(float z) { return z / (1.f + expf(-z)); 
 
 // One warp per token: scores from the router's fp32 logits, then the `top` largest.
 __global__ void __launch_bounds__(128)
-select_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ bias, int n_tokens, int experts,
+select_kernel(const float* __restrict__ logits, int ldl, const float* __restrict__ bias,
+              const float* __restrict__ correction, int n_tokens, int experts,
               int top, int softmax, int renormalize, int groups, int keep, float weight_scale,
               int* __restrict__ chosen, float* __restrict__ weight) {
   pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
@@ -48,6 +49,15 @@ select_kernel(const float* __restrict__ logits, int ldl, const float* __restrict
     for (int e = lane; e < experts; e += 32) sc[e] = 1.f / (1.f + expf(-sc[e]));
   }                              // softmax == 2: the logits themselves are compared
   __syncwarp();
+  // a correction moves the scores for the choice only: the weights come from the scores kept aside
+  float* plain = smem + (size_t)4 * (experts + groups) + (size_t)warp * experts;
+  if (correction != nullptr) {
+    for (int e = lane; e < experts; e += 32) {
+      plain[e] = sc[e];
+      sc[e] += correction[e];
+    }
+    __syncwarp();
+  }
   if (groups > 1 && keep < groups) {
     // what every group is worth, then the groups that are not kept lose their experts
     float* worth = smem + (size_t)4 * experts + (size_t)warp * groups;
@@ -83,6 +93,8 @@ select_kernel(const float* __restrict__ logits, int ldl, const float* __restrict
     if (softmax == 2) {          // the weights are the softmax over the chosen logits only
       if (j == 0) first = best;  // the largest of them
       best = expf(best - first);
+    } else if (correction != nullptr) {
+      best = plain[at];
     }
     if (lane == 0) {
       chosen[(size_t)t * top + j] = at;
@@ -303,7 +315,22 @@ experts_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, flo
   }
 }
 
-// hidden[t, :] += sum_j pair_out[t * top + j, :], j ascending
+// Pairs whose choice is past the last expert are identity experts: pair_out = weight * x[token].
+template <typename T>
+__global__ void experts_identity_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ chosen,
+                                        const float* __restrict__ weight, float* __restrict__ pair_out, long long pairs,
+                                        int width, int experts, int top) {
+  pdl_trigger();
+  pdl_wait();
+  for (long long p = blockIdx.x; p < pairs; p += gridDim.x) {
+    if (chosen[p] < experts) continue;
+    const float w = weight[p];
+    const T* row = x + (size_t)(p / top) * ldx;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) pair_out[(size_t)p * width + c] = w * to_float<T>(row[c]);
+  }
+}
+
+// hidden[t, :] (+)= sum_j pair_out[t * top + j, :], j ascending; top < 0: written, not added (|top| pairs)
 __global__ void experts_combine_kernel(float* __restrict__ hidden, const float* __restrict__ pair_out,
                                        long long total, int width, int top) {
   pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
@@ -313,8 +340,9 @@ __global__ void experts_combine_kernel(float* __restrict__ hidden, const float* 
     const long long t = i / width;
     const int c = (int)(i - t * width);
     float sum = 0.f;
-    for (int j = 0; j < top; ++j) sum += pair_out[((size_t)t * top + j) * width + c];
-    hidden[i] += sum;
+    const int n = top < 0 ? -top : top;
+    for (int j = 0; j < n; ++j) sum += pair_out[((size_t)t * n + j) * width + c];
+    hidden[i] = top < 0 ? sum : hidden[i] + sum;
   }
 }
 
@@ -503,33 +531,50 @@ using namespace leone;
 // logits: fp32 [n_tokens, ldl] (the router's product); chosen, weight: [n_tokens * top].
 // groups <= 1 (or keep == groups): every expert can be chosen.
 // softmax: 0 sigmoid scores, 1 softmax over all experts, 2 the logits are ranked and the weights are the
-// softmax over the chosen ones.  bias: fp32 [experts] added to the logits first, or null.
-extern "C" int leone_experts_select(const float* logits, int ldl, const float* bias, int n_tokens, int experts, int top,
+// softmax over the chosen ones.  bias: fp32 [experts] added to the logits first, or null.  correction: fp32
+// [experts] added to the scores for the choice (and the groups' worth) only, or null: the weights are the
+// scores without it.
+extern "C" int leone_experts_select(const float* logits, int ldl, const float* bias, const float* correction,
+                                    int n_tokens, int experts, int top,
                                     int softmax, int renormalize, int groups, int keep, float weight_scale, int* chosen,
                                     float* weight, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (experts <= 0 || top <= 0 || top > experts || experts > 2048 || ldl < experts) return kRefusedSize;
   if (groups < 1) groups = 1;
   if (experts % groups != 0 || keep < 1 || keep > groups || top > experts / groups * keep) return kRefusedSize;
-  launch_kernel(select_kernel, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * (size_t)(experts + groups), stream,
-      logits, ldl, bias, n_tokens, experts, top, softmax, renormalize, groups, keep, weight_scale, chosen, weight);
+  if (correction != nullptr && softmax == 2) return kRefusedSize;      // ranked logits have no scores to keep aside
+  launch_kernel(select_kernel, dim3((n_tokens + 3) / 4), dim3(128), sizeof(float) * 4 * (size_t)(2 * experts + groups), stream,
+      logits, ldl, bias, correction, n_tokens, experts, top, softmax, renormalize, groups, keep, weight_scale, chosen, weight);
   return launch_result();
 }
 
-// w_gate null: ungated experts (see the top of the file).
+// w_gate null: ungated experts (see the top of the file).  identity: choices `experts .. experts + identity - 1`
+// are experts without tensors whose output is their input (weighted at the output).  fresh: hidden is
+// written, not added to.
 // x: [n_tokens, ldx]; chosen, weight: [n_tokens * top]; scratch: offsets int [experts + 1], order int
 // [pairs], act [pairs, ff] in the run dtype, pair_out fp32 [pairs, width]; hidden fp32 [n_tokens, width].
 extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const void* w_gate, const void* w_up,
                                      const void* w_down, const int* chosen, const float* weight, int n_tokens,
                                      int width, int ff, int experts, int top, int scale_input, int* offsets,
                                      int* order, void* act, float* pair_out, float* hidden, int tensor_cores,
-                                     cudaStream_t stream) {
+                                     int identity, int fresh, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
+  if (identity < 0 || (identity > 0 && scale_input)) return kRefusedSize;
   if (width <= 0 || ff <= 0 || experts <= 0 || top <= 0 || experts > 8192) return kRefusedSize;
   if (w_gate == nullptr && scale_input) return kRefusedSize;      // an ungated expert is weighted at its output
   const long long pairs = (long long)n_tokens * top;
   if (pairs > (1 << 30)) return kRefusedSize;
   launch_kernel(group_pairs_kernel, dim3(1), dim3(1024), sizeof(int) * (size_t)experts, stream, chosen, (int)pairs, experts, offsets, order);
+  if (identity > 0) {
+    const unsigned iblocks = (unsigned)(pairs < 148 * 8 ? pairs : 148 * 8);
+    if (dtype == 0)
+      launch_kernel(experts_identity_kernel<float>, dim3(iblocks), dim3(128), 0, stream, (const float*)x, ldx, chosen, weight,
+                    pair_out, pairs, width, experts, top);
+    else if (dtype == 1)
+      launch_kernel(experts_identity_kernel<__nv_bfloat16>, dim3(iblocks), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx,
+                    chosen, weight, pair_out, pairs, width, experts, top);
+  }
+  const int combine_top = fresh ? -top : top;
   if (tensor_cores && dtype == 1 && width % 8 == 0 && ff % 8 == 0 && ldx % 8 == 0) {
     const long long tiles = (pairs + TM - 1) / TM + (experts < pairs ? experts : pairs);
     if (tiles > 65535) return kRefusedSize;
@@ -555,7 +600,7 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
     const long long total = (long long)n_tokens * width;
     const long long blocks = (total + 255) / 256;
     launch_kernel(experts_combine_kernel, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream, hidden, pair_out,
-                                                                                                total, width, top);
+                                                                                                total, width, combine_top);
     return launch_result();
   }
   // every expert may end with a partly filled tile
@@ -582,6 +627,6 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
   const long long total = (long long)n_tokens * width;
   const long long blocks = (total + 255) / 256;
   launch_kernel(experts_combine_kernel, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream, hidden, pair_out, total,
-                                                                                              width, top);
+                                                                                              width, combine_top);
   return launch_result();
 }

@@ -1,5 +1,6 @@
 // Small kernels shared by several parts: two RMS norms of the same rows in one pass, the squared
-// ReLU, and a product batched over heads.
+// ReLU, a product batched over heads, the norm of a sublayer's output added to the residual stream,
+// elementwise gates.
 #include "common.cuh"
 #include "mma_tile.cuh"
 
@@ -138,6 +139,76 @@ gemm_batched_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
     }
 }
 
+
+// dst[t, :] (+)= coef * (a[t, :] / rms(a[t, :]) * w_a  [+ b[t, :] / rms(b[t, :]) * w_b]), every norm over its own
+// row with eps inside the root.  The norm of a sublayer's *output*, added to the residual stream (or
+// written, if not `accumulate`); with two sources, the normed outputs of two branches side by side.
+// `rounded`: also the new dst row in the run dtype, for the next reader of the stream.
+template <typename TW, typename TR>
+__global__ void __launch_bounds__(256)
+rms_norm_add_kernel(float* __restrict__ dst, const float* __restrict__ a, const TW* __restrict__ w_a,
+                    const float* __restrict__ b, const TW* __restrict__ w_b, int width, float coef, float eps,
+                    int accumulate, TR* __restrict__ rounded) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float scratch[33];
+  const size_t base = (size_t)blockIdx.x * width;
+  float sa = 0.f, sb = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    sa = fmaf(a[base + c], a[base + c], sa);
+    if (b != nullptr) sb = fmaf(b[base + c], b[base + c], sb);
+  }
+  sa = block_sum(sa, scratch);
+  const float ra = 1.f / sqrtf(sa / (float)width + eps);
+  float rb = 0.f;
+  if (b != nullptr) {
+    sb = block_sum(sb, scratch);
+    rb = 1.f / sqrtf(sb / (float)width + eps);
+  }
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v = a[base + c] * ra * to_float<TW>(w_a[c]);
+    if (b != nullptr) v += b[base + c] * rb * to_float<TW>(w_b[c]);
+    v *= coef;
+    if (accumulate) v += dst[base + c];
+    dst[base + c] = v;
+    if (rounded != nullptr) rounded[base + c] = from_float<TR>(v);
+  }
+}
+
+// a[t, c] *= act(gate[t, c]): act 0 sigmoid, 1 silu.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_rows_kernel(T* __restrict__ a, int lda, const T* __restrict__ gate, int ldg, int n_rows, int cols, int act) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = (long long)n_rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / cols;
+    const int c = (int)(i - t * cols);
+    const float z = to_float<T>(gate[t * ldg + c]);
+    const float sg = 1.f / (1.f + expf(-z));
+    a[t * lda + c] = from_float<T>(to_float<T>(a[t * lda + c]) * (act == 1 ? z * sg : sg));
+  }
+}
+
+// out[t, c] = gelu_tanh(z[t, c]) * rows[t, off + c]: a projection's fp32 result gates a slice of a
+// per-token row.  gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gelu_gate_kernel(const float* __restrict__ z, int ldz, const float* __restrict__ rows, int ldr, int off,
+                 T* __restrict__ out, int ldo, int n_rows, int cols) {
+  pdl_trigger();
+  pdl_wait();
+  const long long total = (long long)n_rows * cols;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long t = i / cols;
+    const int c = (int)(i - t * cols);
+    const float v = z[t * ldz + c];
+    const float g = 0.5f * v * (1.f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+    out[t * ldo + c] = from_float<T>(g * rows[t * ldr + off + c]);
+  }
+}
+
 }  // namespace leone
 
 using namespace leone;
@@ -202,4 +273,55 @@ extern "C" int leone_gemm_batched(int dtype, const void* a, const void* w, void*
   else
     return kRefusedDtype;
   return launch_result();
+}
+
+// dst: fp32 [n, width]; a, b: fp32 [n, width] (b and w_b may be null); w in `w_dtype`; rounded: [n, width] in
+// `rounded_dtype`, or null.
+extern "C" int leone_rms_norm_add(float* dst, const float* a, const void* w_a, const float* b, const void* w_b,
+                                  int w_dtype, int n, int width, float coef, float eps, int accumulate, void* rounded,
+                                  int rounded_dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (width <= 0 || (b != nullptr) != (w_b != nullptr)) return kRefusedSize;
+#define NA(TW, TR)                                                                                                    \
+  return launch_kernel(rms_norm_add_kernel<TW, TR>, dim3(n), dim3(256), 0, stream, dst, a, (const TW*)w_a, b,         \
+                       (const TW*)w_b, width, coef, eps, accumulate, (TR*)rounded)
+  if (w_dtype == 0 && rounded_dtype == 0) NA(float, float);
+  if (w_dtype == 0 && rounded_dtype == 1) NA(float, __nv_bfloat16);
+  if (w_dtype == 1 && rounded_dtype == 0) NA(__nv_bfloat16, float);
+  if (w_dtype == 1 && rounded_dtype == 1) NA(__nv_bfloat16, __nv_bfloat16);
+#undef NA
+  return kRefusedDtype;
+}
+
+extern "C" int leone_gate_rows(int dtype, void* a, int lda, const void* gate, int ldg, int n_rows, int cols, int act,
+                               cudaStream_t stream) {
+  if (n_rows <= 0 || cols <= 0) return 0;
+  const long long want = ((long long)n_rows * cols + 255) / 256;
+  const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == 0)
+    return launch_kernel(gate_rows_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)a, lda, (const float*)gate,
+                         ldg, n_rows, cols, act);
+  if (dtype == 1)
+    return launch_kernel(gate_rows_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)a, lda,
+                         (const __nv_bfloat16*)gate, ldg, n_rows, cols, act);
+  return kRefusedDtype;
+}
+
+extern "C" int leone_gelu_gate(int dtype, const float* z, int ldz, const float* rows, int ldr, int off, void* out, int ldo,
+                               int n_rows, int cols, cudaStream_t stream) {
+  if (n_rows <= 0 || cols <= 0) return 0;
+  const long long want = ((long long)n_rows * cols + 255) / 256;
+  const unsigned blocks = (unsigned)(want < 148 * 16 ? want : 148 * 16);
+  if (dtype == 0)
+    return launch_kernel(gelu_gate_kernel<float>, dim3(blocks), dim3(256), 0, stream, z, ldz, rows, ldr, off, (float*)out,
+                         ldo, n_rows, cols);
+  if (dtype == 1)
+    return launch_kernel(gelu_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, z, ldz, rows, ldr, off,
+                         (__nv_bfloat16*)out, ldo, n_rows, cols);
+  return kRefusedDtype;
+}
+
+extern "C" int leone_zero(void* p, long long bytes, cudaStream_t stream) {
+  if (bytes <= 0) return 0;
+  return (int)cudaMemsetAsync(p, 0, (size_t)bytes, stream);
 }

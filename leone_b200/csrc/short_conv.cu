@@ -1,7 +1,8 @@
 // A short causal convolution over time on every channel, with the last taps - 1 inputs of every
 // sequence kept as fixed-size state between steps; and the minGRU recurrence.
 //
-//   leone_short_conv:        y_t[c] = (add_input ? x_t[c] : 0) + sum_j w[c, j] x_(t - taps + 1 + j)[c],
+//   leone_short_conv:        y_t[c] = (add_input & 1 ? x_t[c] : 0) + sum_j w[c, j] x_(t - taps + 1 + j)[c],
+//                            then y * sigmoid(y) if add_input & 2,
 //                            inputs before a sequence's start are zero; an input before the step's
 //                            first token comes from the state
 //   leone_short_conv_state:  the state after the step: the last taps - 1 inputs of every sequence
@@ -55,7 +56,8 @@ short_conv_kernel(const TI* __restrict__ x, int ldx, const float* __restrict__ w
     else v = st[(size_t)(taps - 1 + local - back) * channels + c];
     acc = fmaf(w[(size_t)c * taps + j], v, acc);
   }
-  if (add_input) acc += to_float<TI>(x[(size_t)t * ldx + c]);
+  if (add_input & 1) acc += to_float<TI>(x[(size_t)t * ldx + c]);
+  if (add_input & 2) acc = acc / (1.f + expf(-acc));
   out[(size_t)t * ldo + c] = from_float<TO>(acc);
   if (update_state && taps > 1 && local == 0 && q_start[s + 1] - q_start[s] == 1) {
     for (int r = 0; r + 2 < taps; ++r) st[(size_t)r * channels + c] = st[(size_t)(r + 1) * channels + c];
@@ -161,13 +163,17 @@ short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restric
             for (int e = 0; e < V; ++e) acc[e] = fmaf(wt[j][e], v[i + j][e], acc[e]);
           }
         // the token's own input is v[i + taps - 1]: picked by a static index
-        if (add_input) {
+        if (add_input & 1) {
 #pragma unroll
           for (int j = 0; j < kT; ++j)
             if (j == taps - 1) {
 #pragma unroll
               for (int e = 0; e < V; ++e) acc[e] += v[i + j][e];
             }
+        }
+        if (add_input & 2) {
+#pragma unroll
+          for (int e = 0; e < V; ++e) acc[e] = acc[e] / (1.f + expf(-acc[e]));
         }
         ConvVec<TO, V>::store(out + (size_t)(t0 + i) * ldo + c, acc);
       }
@@ -196,7 +202,8 @@ short_conv_tile_kernel(const TI* __restrict__ x, int ldx, const float* __restric
                                       : st[(size_t)(taps - 1 + local - back) * channels + c + e];
         acc = fmaf(w[(size_t)(c + e) * taps + j], u, acc);
       }
-      if (add_input) acc += to_float<TI>(x[(size_t)t * ldx + c + e]);
+      if (add_input & 1) acc += to_float<TI>(x[(size_t)t * ldx + c + e]);
+      if (add_input & 2) acc = acc / (1.f + expf(-acc));
       out[(size_t)(t * (size_t)ldo) + c + e] = from_float<TO>(acc);
     }
   }

@@ -51,6 +51,8 @@ class StepContext:
         self.logits_out: Optional[torch.Tensor] = None
         self.layer_caches: Dict[int, object] = {}
         self.fixed_shapes = False      # True while a CUDA graph is captured or replayed
+        self.stream_copy = None        # see Model._forward
+        self.token_rows = {}
 
     def cache_view(self, run_position: int):
         """The cache of the layer at this position of the run order (None if it has none)."""

@@ -199,6 +199,8 @@ class Model:
     def _forward(self, ctx) -> Optional[torch.Tensor]:
         rt = self.rt
         hidden = rt.buffer("hidden", ctx.n_tokens, self.hidden_size, torch.float32)
+        ctx.stream_copy = None       # a rounded copy of the stream that some arrangements keep for their readers
+        ctx.token_rows = {}          # per-token rows of further tables that the embedding part gathers
         self.embedding.forward(ctx, hidden)
         origin = None
         if self.injections:
@@ -214,6 +216,9 @@ class Model:
             if pos in self.injections:
                 self.injections[pos].forward(ctx, hidden, origin)
                 pre = None       # a norm folded into the product before it was of the stream as it was
+                ctx.stream_copy = None
+            if not getattr(block, "keeps_stream_copy", False):
+                ctx.stream_copy = None
             if not getattr(block, "chains_norms", False):
                 block.forward(ctx, ctx.cache_view(pos), hidden)
                 pre = None

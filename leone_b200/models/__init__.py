@@ -1,2 +1,2 @@
 """Built-in architectures.  Importing this package registers them."""
-from . import malapel, qwen3, sakinex, sarizen  # noqa: F401
+from . import malapel, qwen3, sakinex, sarizen, ziginex  # noqa: F401

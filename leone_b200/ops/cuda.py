@@ -617,13 +617,14 @@ class CudaOps:
             cache.page_tokens, kp.shape[0], bt.shape[0], _ptr(ctx.status), self._stream()), "attention_latent")
 
     def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False, groups=1,
-                      groups_kept=None, weight_scale=1.0, bias=None, experts=None):
+                      groups_kept=None, weight_scale=1.0, bias=None, experts=None, correction=None):
         """Router logits as an fp32 product (bfloat16 operands multiply exactly in fp32), then the
         scores and the ``top`` best experts of every token (``csrc/experts.cu``), optionally among
         the experts of the ``groups_kept`` best of ``groups`` groups only; the weights times
         ``weight_scale``.  ``softmax``: False (sigmoid scores), True (softmax over all experts) or
         ``"chosen"`` (the logits are ranked, the weights are the softmax over the chosen ones).
-        ``bias``: fp32 ``[experts]`` added to the logits.  ``experts``: the router matrix's first so
+        ``bias``: fp32 ``[experts]`` added to the logits.  ``correction``: fp32 ``[experts]`` added to the scores
+        for the choice (and the groups' worth) only; the weights are the scores without it.  ``experts``: the router matrix's first so
         many rows are experts; further rows are other per-token logits that ride in the same product.
         Returns the fp32 logits ``[n, rows]`` (valid until the next call)."""
         n, width = x.shape
@@ -633,25 +634,28 @@ class CudaOps:
         experts = rows if experts is None else int(experts)
         _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top
               and weight.numel() == n * top and 0 < experts <= rows, "experts_route layout")
-        _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == experts),
-              "experts_route bias")
+        for b in (bias, correction):
+            _need(b is None or (b.dtype == torch.float32 and b.is_contiguous() and b.numel() == experts),
+                  "experts_route bias/correction")
+        _need(correction is None or softmax != "chosen", "experts_route: a correction needs scores")
         logits = self._scratch("router_logits", n, rows, torch.float32)
         self.linear(x, w_router, logits)
         self.launches += 1
         mode = 2 if softmax == "chosen" else (1 if softmax else 0)
-        _check(self.mixers.leone_experts_select(_ptr(logits), logits.stride(0), _ptr(bias), n, experts, top, mode,
+        _check(self.mixers.leone_experts_select(_ptr(logits), logits.stride(0), _ptr(bias), _ptr(correction), n, experts, top, mode,
                                                 1 if renormalize else 0, int(groups), int(groups_kept or groups),
                                                 c_float(weight_scale), _ptr(chosen), _ptr(weight), self._stream()),
                "experts_select")
         return logits
 
     # -- short convolutions with state, the minGRU recurrence, pooled-window attention --------------
-    def short_conv(self, ctx, x, weight, state, out, add_input=False, update_state=False):
+    def short_conv(self, ctx, x, weight, state, out, add_input=False, update_state=False, activation=None):
         """``out_t = (x_t if add_input) + sum_j weight[:, j] x_(t - taps + 1 + j)`` on every channel,
         inputs before the step from ``state`` (fp32 ``[slots, taps - 1, channels]``), which is not
         changed (``csrc/short_conv.cu``) unless ``update_state``, which is for steps in which every
         sequence brings one token: the kernel then leaves the state as :meth:`short_conv_state`
-        would.  ``weight``: fp32 ``[channels, taps]``."""
+        would.  ``weight``: fp32 ``[channels, taps]``.  ``activation``: ``None`` or ``"silu"`` on the result."""
+        _need(activation in (None, "silu"), f"short_conv: activation '{activation}'")
         _need(not update_state or ctx.decode_only, "short_conv: update_state is for steps of one token a sequence")
         n, channels = out.shape
         taps = weight.shape[1]
@@ -662,8 +666,8 @@ class CudaOps:
         self.launches += 1
         _check(self.mixers.leone_short_conv(
             _dt(x.dtype), _dt(out.dtype), _ptr(x), x.stride(0), _ptr(weight), _ptr(state), _ptr(out), out.stride(0),
-            _ptr(ctx.q_start), _ptr(ctx.seq_of_token), _ptr(ctx.slot_ids), n, channels, taps, 1 if add_input else 0,
-            1 if update_state else 0, ctx.n_seqs, state.shape[0] if state is not None else 0, _ptr(ctx.status),
+            _ptr(ctx.q_start), _ptr(ctx.seq_of_token), _ptr(ctx.slot_ids), n, channels, taps,
+            (1 if add_input else 0) | (2 if activation == "silu" else 0), 1 if update_state else 0, ctx.n_seqs, state.shape[0] if state is not None else 0, _ptr(ctx.status),
             self._stream()), "short_conv")
 
     def short_conv_state(self, ctx, x, state):
@@ -837,9 +841,119 @@ class CudaOps:
             "attention_pooled_mma")
         return True
 
-    def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
+    # -- the norm of a sublayer's output, elementwise gates, mixed-head attention, the gated delta rule ----
+    def zero(self, t):
+        """``t = 0`` (a contiguous tensor)."""
+        _need(t.is_contiguous(), "zero needs a contiguous tensor")
+        self.launches += 1
+        _check(self.mixers.leone_zero(_ptr(t), ctypes.c_longlong(t.numel() * t.element_size()), self._stream()), "zero")
+
+    def rms_norm_add(self, dst, a, w_a, eps, b=None, w_b=None, coef=1.0, accumulate=True, rounded=None):
+        """``dst (+)= coef * (rms_norm(a) * w_a [+ rms_norm(b) * w_b])``: fp32 rows, each source normed over
+        its own row; ``rounded``: also the new ``dst`` in another dtype (the stream for its next reader)."""
+        n, width = dst.shape
+        _need(dst.dtype == torch.float32 and dst.is_contiguous() and a.dtype == torch.float32 and a.is_contiguous()
+              and a.shape == dst.shape and w_a.numel() == width and w_a.is_contiguous(), "rms_norm_add layout")
+        if b is not None:
+            _need(b.dtype == torch.float32 and b.is_contiguous() and b.shape == dst.shape and w_b is not None
+                  and w_b.numel() == width and w_b.dtype == w_a.dtype and w_b.is_contiguous(), "rms_norm_add second source")
+        if rounded is not None:
+            _need(rounded.shape == dst.shape and rounded.is_contiguous(), "rms_norm_add rounded copy")
+        self.launches += 1
+        _check(self.mixers.leone_rms_norm_add(
+            _ptr(dst), _ptr(a), _ptr(w_a), _ptr(b), _ptr(w_b if b is not None else None), _dt(w_a.dtype), n, width,
+            c_float(coef), c_float(eps), 1 if accumulate else 0, _ptr(rounded),
+            0 if rounded is None else _dt(rounded.dtype), self._stream()), "rms_norm_add")
+
+    def gate_rows(self, a, gate, act="sigmoid"):
+        """In place: ``a[t, c] *= act(gate[t, c])`` (``"sigmoid"`` or ``"silu"``); both in one dtype."""
+        n, cols = a.shape
+        _need(gate.shape == a.shape and gate.dtype == a.dtype and a.stride(1) == 1 and gate.stride(1) == 1
+              and act in ("sigmoid", "silu"), "gate_rows layout")
+        self.launches += 1
+        _check(self.mixers.leone_gate_rows(_dt(a.dtype), _ptr(a), a.stride(0), _ptr(gate), gate.stride(0), n, cols,
+                                           1 if act == "silu" else 0, self._stream()), "gate_rows")
+
+    def gelu_gate(self, z, rows, offset, out):
+        """``out[t, c] = gelu_tanh(z[t, c]) * rows[t, offset + c]``; ``z`` and ``rows`` fp32."""
+        n, cols = out.shape
+        _need(z.dtype == torch.float32 and rows.dtype == torch.float32 and z.shape == (n, cols) and z.stride(1) == 1
+              and rows.stride(1) == 1 and rows.shape[0] == n and 0 <= offset and offset + cols <= rows.shape[1]
+              and out.stride(1) == 1, "gelu_gate layout")
+        self.launches += 1
+        _check(self.mixers.leone_gelu_gate(_dt(out.dtype), _ptr(z), z.stride(0), _ptr(rows), rows.stride(0), int(offset),
+                                           _ptr(out), out.stride(0), n, cols, self._stream()), "gelu_gate")
+
+    def attention_mixed_heads(self, ctx, q, out, cache, n_q, n_kv, dk, dv, scale, temp, cap, mix, sink, mask, mask_size):
+        """Softmax attention whose scores are mixed across heads before the softmax
+        (``csrc/attention_mixed_heads.cu``): ``raw_g = q_g . k * scale * temp_g``, soft-capped at ``cap``,
+        ``s_h = sum_g mix[h, g] raw_g``, a sink per head in the denominator.  ``temp``, ``mix``, ``sink``: fp32
+        or None; ``cap``: a float or None.  ``q``: ``[n, >= n_q * dk]`` (the heads' queries first in a row)."""
+        n = q.shape[0]
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        _need(out.shape == (n, n_q * dv) and out.is_contiguous() and out.dtype == q.dtype and q.stride(1) == 1
+              and q.shape[1] >= n_q * dk, "attention_mixed_heads: output layout")
+        _need(vp is not None and kp.is_contiguous() and vp.is_contiguous() and kp.dtype == q.dtype == vp.dtype
+              and kp.shape[1] == n_kv and kp.shape[3] == dk and vp.shape[3] == dv, "attention_mixed_heads: cache layout")
+        _need(mask in self._MASKS, f"attention_mixed_heads: mask '{mask}'")
+        for v, count in ((temp, n_q), (mix, n_q * n_q), (sink, n_q)):
+            _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == count),
+                  "attention_mixed_heads: per-head constants")
+        # steps of few tokens: a token's key tiles are dealt to several blocks
+        size = int(mask_size or 0)
+        keys = min(size, ctx.max_ctx_len) if mask != "causal" and size else ctx.max_ctx_len
+        splits = max(1, min(32, -(-keys // 32), 296 // max(n, 1)))
+        partial = None
+        if splits > 1:
+            partial = self._scratch("mixed_heads_partial", n * splits, n_q * (dv + 2), torch.float32)
+            self.launches += 1
+        self.launches += 1
+        _check(self.mixers.leone_attention_mixed_heads(
+            _dt(q.dtype), _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(partial), _ptr(kp), _ptr(vp), _ptr(bt),
+            bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions), n, n_q, n_kv, dk, dv, c_float(scale), _ptr(temp),
+            c_float(cap or 0.0), _ptr(mix), _ptr(sink), self._MASKS[mask], size, cache.page_tokens, kp.shape[0],
+            bt.shape[0], splits, _ptr(ctx.status), self._stream()), "attention_mixed_heads")
+
+    def gated_delta(self, ctx, act, raw, out, state, a_log, dt_bias, heads, kv_heads, dim, vdim, q_off, k_off, v_off,
+                    a_off, b_off, q_scale):
+        """The gated delta rule over the step's tokens (``csrc/gated_delta.cu``).  ``act``: fp32 rows with the
+        activations of q, k (``kv_heads x dim``) and v (``heads x vdim``) at their offsets; ``raw``: fp32 rows with
+        one decay logit and one beta logit per head at ``a_off`` / ``b_off``; ``state``: fp32 ``[slots, heads,
+        dim, vdim]``; ``out``: fp32 ``[n, heads * vdim]``."""
+        n = act.shape[0]
+        _need(act.dtype == torch.float32 and raw.dtype == torch.float32 and act.stride(1) == 1 and raw.stride(1) == 1
+              and raw.shape[0] == n and out.dtype == torch.float32 and out.is_contiguous()
+              and out.shape == (n, heads * vdim), "gated_delta layout")
+        _need(state.dtype == torch.float32 and state.is_contiguous() and tuple(state.shape[1:]) == (heads, dim, vdim)
+              and a_log.dtype == torch.float32 and a_log.numel() == heads and dt_bias.dtype == torch.float32
+              and dt_bias.numel() == heads, "gated_delta state/constants")
+        self.launches += 1
+        _check(self.mixers.leone_gated_delta(
+            _ptr(act), act.stride(0), q_off, k_off, v_off, _ptr(raw), raw.stride(0), a_off, b_off, _ptr(a_log),
+            _ptr(dt_bias), c_float(q_scale), _ptr(out), out.stride(0), _ptr(state), _ptr(ctx.q_start), _ptr(ctx.slot_ids),
+            ctx.n_seqs, heads, kv_heads, dim, vdim, state.shape[0], _ptr(ctx.status), self._stream()), "gated_delta")
+
+    def group_gate_norm(self, o, weight, gate, out, eps, heads, vdim, act="sigmoid"):
+        """``out[t, h, :] = rms_norm(o[t, h, :]) * weight * act(gate[t, h, :])``: every head normed on its own,
+        one weight ``[vdim]`` for all; ``o`` and ``gate`` fp32 (``gate`` may be None)."""
+        n = o.shape[0]
+        _need(o.dtype == torch.float32 and o.stride(1) == 1 and o.shape[1] == heads * vdim and out.shape == o.shape
+              and out.stride(1) == 1 and weight.numel() == vdim and weight.is_contiguous()
+              and act in ("sigmoid", "silu"), "group_gate_norm layout")
+        _need(gate is None or (gate.dtype == torch.float32 and gate.stride(1) == 1 and gate.shape == o.shape),
+              "group_gate_norm gate")
+        self.launches += 1
+        _check(self.mixers.leone_group_gate_norm(
+            _dt(out.dtype), _ptr(o), o.stride(0), n, heads, vdim, _ptr(weight), _dt(weight.dtype), _ptr(gate),
+            0 if gate is None else gate.stride(0), 1 if act == "silu" else 0, _ptr(out), out.stride(0), c_float(eps),
+            self._stream()), "group_gate_norm")
+
+    def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt, identity=0,
+                        fresh=False):
         """``hidden += sum over each token's chosen experts``; scratch comes from ``rt``.
-        ``w_gate`` None: ungated experts, ``W_down max(W_up a, 0)^2``."""
+        ``w_gate`` None: ungated experts, ``W_down max(W_up a, 0)^2``.  ``identity``: choices past the last
+        expert (that many) are experts without tensors whose output is their input.  ``fresh``: ``hidden`` is
+        written, not added to."""
         n, width = x.shape
         experts, ff = w_up.shape[0], w_up.shape[1]
         _need(x.stride(1) == 1 and (w_gate is None or (w_gate.is_contiguous() and w_gate.shape == w_up.shape))
@@ -858,8 +972,8 @@ class CudaOps:
         _check(self.mixers.leone_experts_forward(
             _dt(x.dtype), _ptr(x), x.stride(0), _ptr(w_gate), _ptr(w_up), _ptr(w_down), _ptr(chosen), _ptr(weight), n,
             width, ff, experts, top, 1 if scale_input else 0, _ptr(offsets), _ptr(order), _ptr(act), _ptr(pair_out),
-            _ptr(hidden), 0 if os.environ.get("LEONE_NO_EXPERT_MMA", "0") == "1" else 1, self._stream()),
-            "experts_forward")
+            _ptr(hidden), 0 if os.environ.get("LEONE_NO_EXPERT_MMA", "0") == "1" else 1, int(identity),
+            1 if fresh else 0, self._stream()), "experts_forward")
 
     def sample(self, logits, temperature, seeds, positions, out):
         rows, vocab = logits.shape

@@ -29,6 +29,13 @@ b_head)`` for every seen key on its own, nothing normalised; ``b`` is the tensor
 ``[heads * head_dim]``, multiplied directly) and one over its key heads, before rotation.
 A position encoding that offers ``frequencies()`` instead of a table (``rotary_computed``): the
 kernel forms the angles in fp32, on the first ``rotary_dim`` elements of a head.
+
+Scores mixed across heads (``csrc/attention_mixed_heads.cu``; softmax weights only), each part of it
+present when its parameter is: ``head_temp_name`` (a tensor ``[heads]``: the head's score is multiplied
+by its number), ``score_cap`` (``cap * tanh(score / cap)``), ``head_mix_name`` (a tensor ``[heads,
+heads]``: after scale, temperature and cap, head ``h``'s score becomes ``sum_g M[h, g] score_g``, before
+the mask and the softmax), ``sink_name`` (a tensor ``[heads]``: the softmax's denominator also holds
+``exp(sink_h)``, a member without key or value that is neither scaled nor capped nor mixed).
 """
 from __future__ import annotations
 
@@ -44,6 +51,7 @@ from .base import DeferredNorm, Mixer, PagedKV, WeightSpec
 class Attention(Mixer):
     accepts_deferred_norm = True
     fuses_following_norm = True
+    writes_fresh = True           # forward(..., fresh=True) stores its result instead of adding it
 
     def __init__(self, params, rt, position_encodings=None):
         super().__init__(params, rt)
@@ -68,6 +76,14 @@ class Attention(Mixer):
             raise ValueError(f"attention: mask '{self.mask}' with window {self.window} and chunk {self.chunk}")
         self.bias_name = params.get("bias_name", "bias")
         self.bias = None
+        self.temp_name, self.mix_name = params.get("head_temp_name"), params.get("head_mix_name")
+        self.sink_name = params.get("sink_name")
+        cap = params.get("score_cap")
+        self.score_cap = float(cap) if cap else None
+        self.temp = self.mix = self.sink = None
+        self.mixed = bool(self.temp_name or self.mix_name or self.sink_name or self.score_cap)
+        if self.mixed and self.weights != "softmax":
+            raise ValueError("attention: temperature, cap, mixing and sink go with softmax weights")
         self.scale = float(params.get("scale", 1.0 / math.sqrt(self.d)))
         pe_name = params.get("position_encoding")
         self.pos = (position_encodings or {}).get(pe_name) if pe_name else None
@@ -80,7 +96,7 @@ class Attention(Mixer):
         self.qkv_cols = (self.n_q + self.n_kv) * self.d + self.n_kv * self.dv
         # the layer as the reference has it runs on the kernels tuned for it; anything else on the general ones
         self.general = (self.dv != self.d or self.mask == "chunk" or self.weights != "softmax" or self.norm_whole
-                        or (self.pos is not None and hasattr(self.pos, "frequencies")))
+                        or self.mixed or (self.pos is not None and hasattr(self.pos, "frequencies")))
         if self.general and self.pos is not None and not hasattr(self.pos, "frequencies"):
             raise ValueError("attention: the general kernels take a position encoding that offers its frequencies")
 
@@ -95,6 +111,12 @@ class Attention(Mixer):
                       WeightSpec(self.k_norm_name, (nk,), role="norm", std=0.1)]
         if self.weights == "sigmoid":
             specs.append(WeightSpec(self.bias_name, (self.n_q,), role="vector", std=0.5))
+        if self.temp_name:
+            specs.append(WeightSpec(self.temp_name, (self.n_q,), role="norm", std=0.2))
+        if self.mix_name:
+            specs.append(WeightSpec(self.mix_name, (self.n_q, self.n_q), role="vector", std=0.3))
+        if self.sink_name:
+            specs.append(WeightSpec(self.sink_name, (self.n_q,), role="vector", std=1.0))
         return specs
 
     def load(self, tensors):
@@ -111,6 +133,9 @@ class Attention(Mixer):
             self.k_norm_f32 = self.k_norm_w.float().contiguous()
         if self.weights == "sigmoid":
             self.bias = tensors[self.bias_name].float().contiguous()
+        self.temp = tensors[self.temp_name].float().contiguous() if self.temp_name else None
+        self.mix = tensors[self.mix_name].float().contiguous() if self.mix_name else None
+        self.sink = tensors[self.sink_name].float().contiguous() if self.sink_name else None
 
     def weight_bytes(self):
         return (self.qkv_cols * self.hidden + self.hidden * self.n_q * self.dv) * self.rt.dtype.itemsize
@@ -124,18 +149,21 @@ class Attention(Mixer):
     def cache_request(self):
         return PagedKV(self.n_kv, self.d, self.window, value_head_dim=self.dv)
 
-    def _out_proj(self, attn, hidden, then):
-        """``hidden += W_o attn``; folds the norm that follows (``then``) into the product if it can."""
+    def _out_proj(self, attn, hidden, then, fresh=False):
+        """``hidden += W_o attn`` (``fresh``: ``hidden = W_o attn``); folds the norm that follows (``then``)
+        into the product if it can."""
         ops = self.rt.ops
         n = hidden.shape[0]
-        if then is not None and hasattr(ops, "linear_fuses_norm") and ops.linear_fuses_norm(n, self.w_o):
+        if fresh:
+            ops.linear(attn, self.w_o, hidden)
+        elif then is not None and hasattr(ops, "linear_fuses_norm") and ops.linear_fuses_norm(n, self.w_o):
             then.prepare(self.rt, ops.norm_parts(n, self.hidden))
             ops.linear(attn, self.w_o, hidden, residual=hidden, norm_out=then)
             then.ready = True
         else:
             ops.linear(attn, self.w_o, hidden, residual=hidden)
 
-    def forward(self, ctx, cache, x, hidden, then=None):
+    def forward(self, ctx, cache, x, hidden, then=None, fresh=False):
         rt = self.rt
         n = hidden.shape[0]
         qkv = rt.buffer("qkv", n, self.qkv_cols, rt.dtype)
@@ -147,7 +175,7 @@ class Attention(Mixer):
         else:
             rt.ops.linear(x, self.w_qkv, qkv)
         if self.general:
-            self._forward_general(ctx, cache, qkv, hidden, then)
+            self._forward_general(ctx, cache, qkv, hidden, then, fresh)
             return
         table, rotary_dim, pairing = None, 0, None
         if self.pos is not None:
@@ -166,7 +194,7 @@ class Attention(Mixer):
             rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale, self.window, cache,
                              fuse=dict(q_w=self.q_norm_f32, k_w=self.k_norm_f32, eps=self.eps, rope=table,
                                        write_cache=True, pairing=pairing or "half_split"))
-            self._out_proj(attn, hidden, then)
+            self._out_proj(attn, hidden, then, fresh)
             return
         # q/k norm, rotation and the cache write are one kernel; an encoding without a
         # rotary table is applied by the encoding itself between norm and cache write.
@@ -185,9 +213,9 @@ class Attention(Mixer):
                                       cache if cache.writes else None, **extra)
         rt.ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale,
                          self.window, cache)
-        self._out_proj(attn, hidden, then)
+        self._out_proj(attn, hidden, then, fresh)
 
-    def _forward_general(self, ctx, cache, qkv, hidden, then):
+    def _forward_general(self, ctx, cache, qkv, hidden, then, fresh=False):
         """Masks, weight rules, norms and widths beyond the reference's layer: one kernel norms and
         rotates q and k in fp32 and writes the new keys and values into their pages, one does the
         attention over the pages.  A layer that is causal softmax attention with equal key and
@@ -202,10 +230,13 @@ class Attention(Mixer):
                               self.q_norm_f32 if self.qk_norm else None, self.k_norm_f32 if self.qk_norm else None,
                               self.eps, freqs, pairing, cache if cache.writes else None)
         attn = rt.buffer("attn_out", n, self.n_q * self.dv, rt.dtype)
-        if self.weights == "softmax" and self.mask != "chunk" and self.dv == self.d:
+        size = self.window if self.mask == "window" else (self.chunk if self.mask == "chunk" else 0)
+        if self.mixed:
+            ops.attention_mixed_heads(ctx, qkv, attn, cache, self.n_q, self.n_kv, self.d, self.dv, self.scale, self.temp,
+                                      self.score_cap, self.mix, self.sink, self.mask, int(size or 0))
+        elif self.weights == "softmax" and self.mask != "chunk" and self.dv == self.d:
             ops.attention(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.scale, self.window, cache)
         else:
-            size = self.window if self.mask == "window" else (self.chunk if self.mask == "chunk" else 0)
             ops.attention_masked(ctx, qkv, attn, self.n_q, self.n_kv, self.d, self.dv, self.scale, self.mask,
                                  int(size or 0), self.weights, self.bias, cache)
-        self._out_proj(attn, hidden, then)
+        self._out_proj(attn, hidden, then, fresh)

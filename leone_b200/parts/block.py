@@ -120,3 +120,66 @@ class ParallelBlock(Block):
             xb = b.forward(ctx, hidden, out_name="normed_b")
         self.mixer.forward(ctx, cache, xa, hidden)
         self.feed_forward.forward(ctx, xb, hidden)
+
+
+@BLOCKS.register("post_norm")
+class PostNormBlock(Block):
+    """``h += norm_a(mixer(h)); h += norm_b(ffn(h))``: a sublayer reads the residual stream itself, and the
+    norm is on what it gives back.  Then, if the layer has one, a further part ``after`` (registry
+    ``feed_forward``) that reads the stream and adds to it on its own terms.  A layer without a
+    feed-forward (and without its norm) is the mixer's half only.
+
+    The sublayer writes into a branch buffer: a part that declares ``writes_fresh`` is told so
+    (``fresh=True``) and stores its result there; any other part adds into the zeroed buffer.  In a
+    bfloat16 run the sublayers read the stream rounded to bfloat16; the kernel that adds a normed branch
+    leaves that rounded copy for the next reader (``ctx.stream_copy``), so it is formed by a kernel of
+    its own only where a block of another kind ran before."""
+
+    keeps_stream_copy = True
+
+    def __init__(self, mixer, feed_forward, mixer_norm, ffn_norm, after=None, **extra):
+        if mixer_norm is None or (feed_forward is None) != (ffn_norm is None) or extra:
+            raise ValueError("the post_norm arrangement is mixer, norm and, optionally, feed-forward, norm and a part "
+                             "after them: it takes exactly those parts")
+        for norm in (mixer_norm, ffn_norm):
+            if norm is not None and not hasattr(norm, "add_normed"):
+                raise ValueError("the post_norm arrangement needs norms that can add a normed branch to the stream")
+        super().__init__(mixer, feed_forward, mixer_norm, ffn_norm)
+        self.after = after
+
+    @staticmethod
+    def _read(ctx, rt, hidden):
+        """The stream as the sublayers' products read it: itself in a 32-bit run, else its rounded copy."""
+        if rt.dtype == torch.float32:
+            return hidden, None
+        copy = rt.buffer("stream_rounded", hidden.shape[0], hidden.shape[1], rt.dtype)
+        if getattr(ctx, "stream_copy", None) is not copy:
+            rt.ops.convert(hidden, copy)
+            ctx.stream_copy = copy
+        return copy, copy
+
+    @staticmethod
+    def _run(part, rt, branch, *args):
+        if getattr(part, "writes_fresh", False):
+            part.forward(*args, branch, fresh=True)
+        else:
+            rt.ops.zero(branch)
+            part.forward(*args, branch)
+
+    def forward(self, ctx, cache, hidden):
+        rt = self.mixer.rt
+        branch = rt.buffer("sublayer_out", hidden.shape[0], hidden.shape[1], torch.float32)
+        x, copy = self._read(ctx, rt, hidden)
+        self._run(self.mixer, rt, branch, ctx, cache, x)
+        self.mixer_norm.add_normed(ctx, branch, hidden, rounded=copy)
+        if self.feed_forward is not None:
+            x, copy = self._read(ctx, rt, hidden)
+            self._run(self.feed_forward, rt, branch, ctx, x)
+            self.ffn_norm.add_normed(ctx, branch, hidden, rounded=copy)
+        if self.after is not None:
+            x, copy = self._read(ctx, rt, hidden)
+            if getattr(self.after, "keeps_stream_copy", False):
+                self.after.forward(ctx, x, hidden, rounded=copy)
+            else:
+                self.after.forward(ctx, x, hidden)
+                ctx.stream_copy = None

@@ -5,6 +5,8 @@ The reference gathers the row without a factor and treats an id outside the tabl
 (default 1) is this part's own parameter for models that multiply their embeddings.  ``norm``
 (a mapping with ``name``, ``eps`` and optionally ``weight_offset``; default none) adds an RMS norm
 of the gathered rows, in fp32, with a weight of the part's own: ``h = rms_norm(scale * E[id])``.
+``side_tables`` (a list of ``{"name", "width"}``; default none): further tables ``[vocab, width]`` whose
+rows of the step's tokens are gathered too (fp32) and offered to the layers as ``ctx.token_rows[name]``.
 """
 from __future__ import annotations
 
@@ -26,20 +28,24 @@ class TokenEmbedding(Embedding):
         self.norm_eps = float(norm["eps"]) if norm else 0.0
         self.norm_offset = float(norm.get("weight_offset", 0.0)) if norm else 0.0
         self.norm_weight = None
+        self.side_tables = [(t["name"], int(t["width"])) for t in params.get("side_tables") or ()]
+        self.side_weights = {}
 
     def weight_specs(self):
         specs = [WeightSpec(self.name, (self.vocab, self.hidden), role="embedding")]
+        specs += [WeightSpec(name, (self.vocab, width), role="embedding") for name, width in self.side_tables]
         if self.norm_name:
             specs.append(WeightSpec(self.norm_name, (self.hidden,), role="vector" if self.norm_offset else "norm", std=0.1))
         return specs
 
     def load(self, tensors):
         self.weight = tensors[self.name]
+        self.side_weights = {name: tensors[name] for name, _ in self.side_tables}
         if self.norm_name:
             self.norm_weight = (tensors[self.norm_name].float() + self.norm_offset).contiguous()
 
     def scratch_bytes(self, max_tokens):
-        return max_tokens * self.hidden * 4 if self.norm_name else 0
+        return max_tokens * 4 * ((self.hidden if self.norm_name else 0) + sum(w for _, w in self.side_tables))
 
     def table(self):
         return self.weight
@@ -54,3 +60,7 @@ class TokenEmbedding(Embedding):
             self.rt.ops.embedding(self.weight, ctx.token_ids, rows, ctx.status, self.scale)
         if self.norm_name:
             self.rt.ops.rms_norm(rows, self.norm_weight, hidden, self.norm_eps)
+        for name, width in self.side_tables:
+            side = self.rt.buffer(f"token_rows_{name}", hidden.shape[0], width, hidden.dtype)
+            self.rt.ops.embedding(self.side_weights[name], ctx.token_ids, side, ctx.status)
+            ctx.token_rows[name] = side

@@ -20,6 +20,11 @@ equal runs of neighbours, a run is worth its largest score, the ``groups_kept`` 
 lowest index among equal ones); ``weight_scale`` multiplies the chosen weights (after an optional
 renormalisation).
 
+``correction_name``: a tensor ``[experts]`` added to the scores for the choice (and for a group's worth)
+only; the weights stay the scores without it.  ``identity``: the router has that many outputs past the
+experts whose "expert" has no tensors and gives back its input (times the weight); they take part in
+the scores, the groups and the choice like any other.
+
 Experts' matrices are stacked at load time (``[experts, ff, hidden]`` twice and ``[experts, hidden,
 ff]``); the pairs (token, choice) are grouped by expert on the device and the grouped products run
 over them, so nothing is read back by the host and a captured decode step can replay it.
@@ -34,6 +39,8 @@ from .base import FeedForward, WeightSpec
 
 @FEED_FORWARDS.register("routed_experts")
 class RoutedExperts(FeedForward):
+    writes_fresh = True           # forward(..., fresh=True) stores its result instead of adding it
+
     def __init__(self, params, rt):
         super().__init__(params, rt)
         self.hidden = int(params["hidden_size"])
@@ -53,17 +60,23 @@ class RoutedExperts(FeedForward):
         self.router_bias_name = params.get("router_bias_name")
         self.shared_gate_name = params.get("shared_gate_name") if self.shared_ff else None
         self.router_bias = None
+        self.correction_name = params.get("correction_name")
+        self.correction = None
+        self.identity = int(params.get("identity", 0))
+        self.outputs = self.experts + self.identity          # what the router chooses among
+        if self.identity and (self.scale == "input" or shared):
+            raise ValueError("routed experts: identity experts are weighted at their output and go without a shared expert")
         if self.score not in ("sigmoid", "softmax", "softmax_chosen") or self.scale not in ("input", "output"):
             raise ValueError(f"routed experts: score '{self.score}' / scale '{self.scale}'")
         if self.form not in ("gated_silu", "relu_squared"):
             raise ValueError(f"routed experts: expert form '{self.form}'")
-        if self.groups < 1 or self.experts % self.groups or not 0 < self.groups_kept <= self.groups or \
-                self.top > self.experts // self.groups * self.groups_kept:
+        if self.groups < 1 or self.outputs % self.groups or not 0 < self.groups_kept <= self.groups or \
+                self.top > self.outputs // self.groups * self.groups_kept:
             raise ValueError(f"routed experts: {self.experts} experts in {self.groups} groups, {self.groups_kept} kept, "
                              f"{self.top} chosen")
         if self.form == "relu_squared" and self.scale == "input":
             raise ValueError("routed experts: ungated experts are weighted at their output")
-        if not 0 < self.top <= self.experts:
+        if not 0 < self.top <= self.outputs:
             raise ValueError(f"routed experts: top {self.top} of {self.experts}")
         self.router_name = params.get("router_name", "router")
         self.expert_pattern = params.get("expert_pattern", "e{}.{}")      # (index, gate|up|down)
@@ -84,9 +97,11 @@ class RoutedExperts(FeedForward):
                 specs.append(WeightSpec(self._expert(e, "gate"), (self.ff, self.hidden)))
             specs += [WeightSpec(self._expert(e, "up"), (self.ff, self.hidden)),
                       WeightSpec(self._expert(e, "down"), (self.hidden, self.ff))]
-        specs.append(WeightSpec(self.router_name, (self.experts, self.hidden)))
+        specs.append(WeightSpec(self.router_name, (self.outputs, self.hidden)))
         if self.router_bias_name:
-            specs.append(WeightSpec(self.router_bias_name, (self.experts,), role="vector", std=0.5))
+            specs.append(WeightSpec(self.router_bias_name, (self.outputs,), role="vector", std=0.5))
+        if self.correction_name:
+            specs.append(WeightSpec(self.correction_name, (self.outputs,), role="vector", std=0.05))
         if self.shared_gate_name:
             specs.append(WeightSpec(self.shared_gate_name, (1, self.hidden)))
         if self.shared_ff:
@@ -105,6 +120,8 @@ class RoutedExperts(FeedForward):
         self.w_router = self.rt.ops.prepare_matrix(router.contiguous())
         if self.router_bias_name:
             self.router_bias = tensors[self.router_bias_name].float().contiguous()
+        if self.correction_name:
+            self.correction = tensors[self.correction_name].float().contiguous()
         if self.shared_ff:
             ops = self.rt.ops
             self.w_shared_gate_up = ops.prepare_gate_up(tensors[self.shared_pattern.format("gate")],
@@ -114,7 +131,7 @@ class RoutedExperts(FeedForward):
     def weight_bytes(self):
         # a decode step reads the router, the shared expert and `top` experts per token (at most all)
         per_expert = (3 if self.gated else 2) * self.ff * self.hidden
-        return (self.experts * self.hidden + 3 * (self.shared_ff or 0) * self.hidden
+        return (self.outputs * self.hidden + 3 * (self.shared_ff or 0) * self.hidden
                 + self.top * per_expert) * self.rt.dtype.itemsize
 
     def scratch_bytes(self, max_tokens):
@@ -126,7 +143,7 @@ class RoutedExperts(FeedForward):
     def load_transient_bytes(self):
         return (3 if self.gated else 2) * self.experts * self.ff * self.hidden * self.rt.dtype.itemsize
 
-    def forward(self, ctx, x, hidden):
+    def forward(self, ctx, x, hidden, fresh=False):
         rt, ops = self.rt, self.rt.ops
         n = hidden.shape[0]
         pairs = n * self.top
@@ -137,11 +154,16 @@ class RoutedExperts(FeedForward):
         if self.groups > 1 or scale != 1.0:
             extra = dict(groups=self.groups, groups_kept=self.groups_kept, weight_scale=scale)
         if self.router_bias is not None or self.shared_gate_name:
-            extra.update(bias=self.router_bias, experts=self.experts)
+            extra.update(bias=self.router_bias, experts=self.outputs)
+        if self.correction is not None:
+            extra.update(correction=self.correction)
         softmax = "chosen" if self.score == "softmax_chosen" else self.score == "softmax"
         logits = ops.experts_route(x, self.w_router, chosen, weight, self.top, softmax, self.renormalize, **extra)
+        more = {}
+        if self.identity or fresh:
+            more = dict(identity=self.identity, fresh=fresh)
         ops.experts_forward(x, self.w_gate, self.w_up, self.w_down, chosen, weight, self.top,
-                            self.scale == "input", hidden, rt)
+                            self.scale == "input", hidden, rt, **more)
         if self.shared_ff:
             act = rt.buffer("experts_shared_act", n, self.shared_ff, rt.dtype)
             ops.linear_swiglu(x, self.w_shared_gate_up, act)

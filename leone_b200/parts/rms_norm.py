@@ -43,6 +43,11 @@ class RMSNorm(Norm):
         self.rt.ops.rms_norm(hidden, self.weight, out, self.eps, rows)
         return out
 
+    def add_normed(self, ctx, branch, hidden, rounded=None):
+        """``hidden += rms_norm(branch) * weight``: this norm on a sublayer's output ``branch`` (fp32), added
+        to the residual stream; ``rounded``: also the new stream in another dtype."""
+        self.rt.ops.rms_norm_add(hidden, branch, self.weight, self.eps, rounded=rounded)
+
     def forward_pair(self, ctx, hidden, other: "RMSNorm"):
         """This norm and ``other`` (same size and eps) of the same rows in one pass."""
         n = hidden.shape[0]

@@ -4,19 +4,37 @@
 (tensor names, sizes, an output scale if it has one), reads the same normed rows and adds its own
 output to the residual stream; each owns the cache it asks for.  ``branches`` is a list of ``{"name",
 "kind", "params"}``; the caches arrive under the branches' names.
+
+``combine = "normed_mean"``: ``hidden += (1 / branches) sum_b rms_norm(mixer_b(x)) * w_b`` instead: every
+branch's output is RMS-normed over the model width (``norm_eps``) with a weight of its own (the branch's
+``norm_name``) before the mean is taken.
 """
 from __future__ import annotations
 
 import inspect
 
+import torch
+
 from ..registry import MIXERS
-from .base import CacheBundle, Mixer
+from .base import CacheBundle, Mixer, WeightSpec
 
 
 @MIXERS.register("side_by_side")
 class SideBySide(Mixer):
+    writes_fresh = True           # forward(..., fresh=True) stores its result instead of adding it
+
     def __init__(self, params, rt, position_encodings=None):
         super().__init__(params, rt)
+        self.combine = params.get("combine", "sum")
+        if self.combine not in ("sum", "normed_mean"):
+            raise ValueError(f"side_by_side: combine '{self.combine}'")
+        self.norm_names = [b.get("norm_name") for b in params["branches"]]
+        self.norm_weights = []
+        if self.combine == "normed_mean":
+            self.hidden = int(params["hidden_size"])
+            self.eps = float(params["norm_eps"])
+            if not all(self.norm_names):
+                raise ValueError("side_by_side: the normed mean needs a norm_name for every branch")
         self.branches = []
         for b in params["branches"]:
             cls = MIXERS.get(b["kind"])
@@ -29,11 +47,16 @@ class SideBySide(Mixer):
             raise ValueError("side_by_side: branches need distinct names")
 
     def weight_specs(self):
-        return [s for _, part in self.branches for s in part.weight_specs()]
+        specs = [s for _, part in self.branches for s in part.weight_specs()]
+        if self.combine == "normed_mean":
+            specs += [WeightSpec(name, (self.hidden,), role="norm", std=0.1) for name in self.norm_names]
+        return specs
 
     def load(self, tensors):
         for _, part in self.branches:
             part.load({s.name: tensors[s.name] for s in part.weight_specs()})
+        if self.combine == "normed_mean":
+            self.norm_weights = [tensors[name] for name in self.norm_names]
 
     def weight_bytes(self):
         return sum(part.weight_bytes() for _, part in self.branches if hasattr(part, "weight_bytes"))
@@ -47,6 +70,26 @@ class SideBySide(Mixer):
     def cache_request(self):
         return CacheBundle({name: part.cache_request() for name, part in self.branches})
 
-    def forward(self, ctx, cache, x, hidden):
-        for name, part in self.branches:
-            part.forward(ctx, cache[name], x, hidden)
+    def forward(self, ctx, cache, x, hidden, fresh=False):
+        if self.combine == "sum":
+            if fresh:
+                self.rt.ops.zero(hidden)
+            for name, part in self.branches:
+                part.forward(ctx, cache[name], x, hidden)
+            return
+        rt, ops = self.rt, self.rt.ops
+        outs = []
+        for i, (name, part) in enumerate(self.branches):
+            out = rt.buffer(f"side_by_side_{i}", hidden.shape[0], hidden.shape[1], torch.float32)
+            if getattr(part, "writes_fresh", False):
+                part.forward(ctx, cache[name], x, out, fresh=True)
+            else:
+                ops.zero(out)
+                part.forward(ctx, cache[name], x, out)
+            outs.append(out)
+        coef, w = 1.0 / len(outs), self.norm_weights
+        # the normed outputs two at a time: one pass over the rows for a pair of branches
+        for i in range(0, len(outs), 2):
+            pair = i + 1 < len(outs)
+            ops.rms_norm_add(hidden, outs[i], w[i], self.eps, b=outs[i + 1] if pair else None,
+                             w_b=w[i + 1] if pair else None, coef=coef, accumulate=not (fresh and i == 0))

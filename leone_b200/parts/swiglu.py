@@ -20,6 +20,7 @@ from .base import DeferredNorm, FeedForward, WeightSpec
 class SwiGLU(FeedForward):
     accepts_deferred_norm = True
     fuses_following_norm = True
+    writes_fresh = True           # forward(..., fresh=True) stores its result instead of adding it
 
     def __init__(self, params, rt):
         super().__init__(params, rt)
@@ -56,7 +57,7 @@ class SwiGLU(FeedForward):
     def load_transient_bytes(self):
         return 2 * self.inter * self.hidden * self.rt.dtype.itemsize       # gate and up beside their interleaved copy
 
-    def forward(self, ctx, x, hidden, then=None):
+    def forward(self, ctx, x, hidden, then=None, fresh=False):
         n = hidden.shape[0]
         ops = self.rt.ops
         act = self.rt.buffer("ffn_act", n, self.inter, self.rt.dtype)
@@ -73,4 +74,4 @@ class SwiGLU(FeedForward):
             ops.linear(act, self.w_down, hidden, residual=hidden, norm_out=then)
             then.ready = True
         else:
-            ops.linear(act, self.w_down, hidden, residual=hidden)
+            ops.linear(act, self.w_down, hidden, residual=None if fresh else hidden)

@@ -273,7 +273,7 @@ class EmulatedOps:
         out.copy_(res.reshape(n, heads * dv).to(out.dtype))
 
     def experts_route(self, x, w_router, chosen, weight, top, softmax=False, renormalize=False, groups=1,
-                      groups_kept=None, weight_scale=1.0, bias=None, experts=None):
+                      groups_kept=None, weight_scale=1.0, bias=None, experts=None, correction=None):
         logits = x.float() @ w_router.float().t()
         z = logits if experts is None else logits[:, :experts]
         if bias is not None:
@@ -284,11 +284,16 @@ class EmulatedOps:
             weight.copy_(torch.softmax(val, dim=-1).reshape(-1) * weight_scale)
             return logits
         s = torch.softmax(z, dim=-1) if softmax else torch.sigmoid(z)
+        plain_scores = s
+        if correction is not None:
+            s = s + correction
         if groups > 1 and (groups_kept or groups) < groups:
             worth = s.view(s.shape[0], groups, -1).max(dim=-1).values
             kept = torch.zeros_like(worth, dtype=torch.bool).scatter_(1, torch.topk(worth, groups_kept, dim=-1).indices, True)
             s = s.masked_fill(~kept.repeat_interleave(s.shape[1] // groups, dim=1), float("-inf"))
         val, idx = torch.topk(s, top, dim=-1)
+        if correction is not None:
+            val = torch.gather(plain_scores, 1, idx)
         if renormalize:
             val = val / val.sum(dim=-1, keepdim=True)
         chosen.copy_(idx.reshape(-1).to(torch.int32))
@@ -310,8 +315,11 @@ class EmulatedOps:
                 out[a + t] = (weight.t() * hist[t:t + taps]).sum(dim=0)
         return out + x if add_input else out
 
-    def short_conv(self, ctx, x, weight, state, out, add_input=False, update_state=False):
-        out.copy_(self._conv_rows(ctx, x, weight, state, add_input).to(out.dtype))
+    def short_conv(self, ctx, x, weight, state, out, add_input=False, update_state=False, activation=None):
+        rows = self._conv_rows(ctx, x, weight, state, add_input)
+        if activation == "silu":
+            rows = torch.nn.functional.silu(rows)
+        out.copy_(rows.to(out.dtype))
         if update_state and state is not None:
             self.short_conv_state(ctx, x, state)
 
@@ -404,13 +412,101 @@ class EmulatedOps:
                 res[t, h] = (w[:, None] * vals[:, h // g, :]).sum(0)
         out.copy_((res * out_scale).reshape(n, n_q * dv).to(out.dtype))
 
-    def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt):
+    # -- the norm of a sublayer's output, elementwise gates, mixed-head attention, the gated delta rule ----
+    def zero(self, t):
+        t.zero_()
+
+    def rms_norm_add(self, dst, a, w_a, eps, b=None, w_b=None, coef=1.0, accumulate=True, rounded=None):
+        def normed(x, w):
+            return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * w.float()
+        v = normed(a, w_a)
+        if b is not None:
+            v = v + normed(b, w_b)
+        v = coef * v
+        dst.copy_(dst + v if accumulate else v)
+        if rounded is not None:
+            rounded.copy_(dst.to(rounded.dtype))
+
+    def gate_rows(self, a, gate, act="sigmoid"):
+        g = gate.float()
+        f = torch.sigmoid(g) if act == "sigmoid" else g * torch.sigmoid(g)
+        a.copy_((a.float() * f).to(a.dtype))
+
+    def gelu_gate(self, z, rows, offset, out):
+        g = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3)))
+        out.copy_((g * rows[:, offset:offset + out.shape[1]]).to(out.dtype))
+
+    def attention_mixed_heads(self, ctx, q, out, cache, n_q, n_kv, dk, dv, scale, temp, cap, mix, sink, mask, mask_size):
+        n = q.shape[0]
+        qf = q.float()[:, :n_q * dk].view(n, n_q, dk)
+        g = n_q // n_kv
+        pt = cache.page_tokens
+        res = torch.zeros(n, n_q, dv)
+        for t, (p, s) in enumerate(zip(ctx.positions.tolist(), ctx.seq_of_token.tolist())):
+            lo = {"causal": 0, "window": max(0, p - mask_size + 1) if mask_size else 0,
+                  "chunk": (p // mask_size) * mask_size if mask_size else 0}[mask]
+            idx = torch.arange(lo, p + 1)
+            pages = cache.block_table[s, idx // pt].long()
+            assert (pages >= 0).all(), "read from a block without a page"
+            keys = cache.k_pool[pages, :, idx % pt, :].float().repeat_interleave(g, dim=1)      # [ctx, n_q, dk]
+            vals = cache.v_pool[pages, :, idx % pt, :].float().repeat_interleave(g, dim=1)
+            sc = torch.einsum("jhd,hd->hj", keys, qf[t]) * scale
+            if temp is not None:
+                sc = sc * temp[:, None]
+            if cap:
+                sc = cap * torch.tanh(sc / cap)
+            if mix is not None:
+                sc = mix @ sc
+            if sink is not None:
+                sc = torch.cat([sc, sink[:, None]], dim=1)
+            w = torch.softmax(sc, dim=1)[:, :idx.numel()]
+            res[t] = torch.einsum("hj,jhv->hv", w, vals)
+        out.copy_(res.reshape(n, n_q * dv).to(out.dtype))
+
+    def gated_delta(self, ctx, act, raw, out, state, a_log, dt_bias, heads, kv_heads, dim, vdim, q_off, k_off, v_off,
+                    a_off, b_off, q_scale):
+        rep = heads // kv_heads
+        bounds, slots = ctx.q_start.tolist(), ctx.slot_ids.tolist()
+
+        def unit(x):
+            return x * torch.rsqrt((x * x).sum(dim=-1, keepdim=True) + 1e-6)
+        for s, slot in enumerate(slots):
+            st = state[slot]
+            for t in range(bounds[s], bounds[s + 1]):
+                q = (unit(act[t, q_off:q_off + kv_heads * dim].view(kv_heads, dim)) * q_scale).repeat_interleave(rep, dim=0)
+                k = unit(act[t, k_off:k_off + kv_heads * dim].view(kv_heads, dim)).repeat_interleave(rep, dim=0)
+                v = act[t, v_off:v_off + heads * vdim].view(heads, vdim)
+                beta = torch.sigmoid(raw[t, b_off:b_off + heads])
+                g = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(raw[t, a_off:a_off + heads] + dt_bias))
+                st = g[:, None, None] * st
+                u = beta[:, None] * (v - torch.einsum("hdv,hd->hv", st, k))
+                st = st + k[:, :, None] * u[:, None, :]
+                out[t] = torch.einsum("hdv,hd->hv", st, q).reshape(-1)
+            state[slot] = st
+
+    def group_gate_norm(self, o, weight, gate, out, eps, heads, vdim, act="sigmoid"):
+        n = o.shape[0]
+        x = o.view(n, heads, vdim)
+        y = x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * weight.float()
+        if gate is not None:
+            g = gate.float().reshape(n, heads, vdim)
+            y = y * (torch.sigmoid(g) if act == "sigmoid" else g * torch.sigmoid(g))
+        out.copy_(y.reshape(n, heads * vdim).to(out.dtype))
+
+    def experts_forward(self, x, w_gate, w_up, w_down, chosen, weight, top, scale_input, hidden, rt, identity=0,
+                        fresh=False):
         n = x.shape[0]
         silu = torch.nn.functional.silu
         xf = x.float()
+        if fresh:
+            hidden.zero_()
         for t in range(n):
             for j in range(top):
                 e, w = int(chosen[t * top + j]), weight[t * top + j]
+                if e >= w_up.shape[0]:
+                    assert e < w_up.shape[0] + identity
+                    hidden[t] += xf[t] * w
+                    continue
                 a = xf[t] * w if scale_input else xf[t]
                 if w_gate is None:
                     y = w_down[e].float() @ (torch.relu(w_up[e].float() @ a) ** 2)
