@@ -7,8 +7,8 @@ Prints one JSON line.  ``--gpus N`` with N > 1 prints one line saying that this 
 on one GPU and exits with 2.  ``--impl reference`` prints why the reference cannot run here.
 ``--shape qwen3-32b | qwen3-1.7b``, ``--batch``, ``--context`` measure the other baseline
 configurations; ``--workload serving`` runs many requests through the scheduler; ``--design sarizen``,
-``--design malapel`` or ``--design sakinex`` measures that design beside the dense decoder at equal size
-(the last also beside the looped design with windows and routed experts, its closest relative).
+``--design malapel``, ``--design sakinex`` or ``--design ziginex`` measures that design beside the dense
+decoder at equal size (the last two also beside their closest relatives among the other designs).
 """
 import argparse
 import os
@@ -34,7 +34,7 @@ def main() -> int:
     ap.add_argument("--workload", default="decode", choices=["decode", "serving"],
                     help="serving: many requests with mixed prompt lengths through the scheduler (its own JSON line)")
     ap.add_argument("--requests", type=int, default=64, help="serving: concurrent requests")
-    ap.add_argument("--design", default=None, choices=["sarizen", "malapel", "sakinex"],
+    ap.add_argument("--design", default=None, choices=["sarizen", "malapel", "sakinex", "ziginex"],
                     help="another design at layer sizes like a real model's beside the dense decoder at equal "
                          "size: prefill and decode tokens/s and time per kind of kernel (its own JSON line)")
     ap.add_argument("--size", default="small", choices=["small", "medium"], help="--design: which layer sizes")

@@ -446,6 +446,30 @@ def _malapel_like_sakinex(width: int, runs: int, heads: int, experts: int, top: 
             "layers": [{"type": "attention_3", "mixer": m, "mlp": moe} for _ in range(runs - 2)]}
 
 
+def _ziginex_shape(width: int, layers: int, heads: int, experts: int, top: int, expert_ff: int, shared_ff: int,
+                   kv_rank: int, chunk: int, vocab: int) -> dict:
+    """Layer sizes that resemble a real model's: three parallel layers (attention in chunks with mixed
+    scores, four query heads to a key/value head, beside a gated delta rule with two value heads to a
+    key head and convolutions of four taps) to every latent-attention layer; a dense feed-forward in the
+    first layer, elsewhere routed experts with four identity experts among the router's outputs, chosen
+    from the best two of four groups; a token gate of 256 per layer."""
+    left = {"heads": heads, "kv_heads": max(heads // 4, 1), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "softcap": 30.0, "mask": {"size": chunk}, "rot": {"base": 10000.0, "dims": 64}}
+    right = {"heads": heads, "kv_heads": max(heads // 2, 1), "dim": 128, "vdim": 128, "conv": 4}
+    latent = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": kv_rank, "q_rank": 3 * kv_rank // 2,
+              "scale": 192 ** -0.5,
+              "rot": {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "expert": {"ff": expert_ff},
+           "router": {"experts": experts, "identity": 4, "top": top, "groups": {"count": 4, "keep": 2}}}
+    out = []
+    for i in range(layers):
+        attn = i % 4 == 3
+        out.append({"type": "latent_attention" if attn else "parallel", "mixer": latent if attn else {"left": left, "right": right},
+                    "mlp": {"kind": "dense", "ff": top * expert_ff + shared_ff} if i == 0 else moe})
+    return {"architecture": "Ziginex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "token_side": {"dim": 256},
+            "layers": out}
+
+
 SAKINEX_SIZES = {
     # name: (width, layer runs, heads, experts, top, expert ff, shared ff, window, pool, vocab)
     "small": (2048, 8, 16, 32, 4, 768, 1024, 1024, 64, 32768),
@@ -478,7 +502,8 @@ class _OpTimer:
                  "linear_attention", "gate_norm", "latent_prepare", "attention_latent", "experts_route",
                  "experts_forward", "attention", "qk_norm_rope_write", "embedding", "logit_post", "attention_prepare",
                  "attention_masked", "convert", "short_conv", "short_conv_state", "min_gru", "scale_rows", "add_scaled",
-                 "attention_pooled_prepare", "attention_pool_blocks", "attention_pooled"]
+                 "attention_pooled_prepare", "attention_pool_blocks", "attention_pooled", "zero", "rms_norm_add",
+                 "gate_rows", "gelu_gate", "attention_mixed_heads", "gated_delta", "group_gate_norm"]
         for name in names:
             fn = getattr(self.ops, name, None)
             if fn is None:
@@ -560,6 +585,9 @@ def compare_designs(design: str = "sarizen", size: str = "small", steps: int = 6
         width, layers, heads, experts, top, expert_ff, shared_ff, window, pool, vocab = SAKINEX_SIZES[size]
         raw = _sakinex_shape(width, layers, heads, experts, top, expert_ff, shared_ff, window, pool, vocab)
         rank = 0
+    elif design == "ziginex":
+        width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab = DESIGN_SIZES[size]
+        raw = _ziginex_shape(width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab)
     else:
         raise ValueError(f"unknown design '{design}'")
     dense = dict(architectures=["Qwen3ForCausalLM"], num_hidden_layers=layers, hidden_size=width,
@@ -576,6 +604,8 @@ def compare_designs(design: str = "sarizen", size: str = "small", steps: int = 6
     others = [("qwen3", dense)]
     if design == "sakinex":     # its closest existing model is the looped design with windows and routed experts
         others.insert(0, ("malapel", _malapel_like_sakinex(width, layers, heads, experts, top, expert_ff, window, vocab)))
+    if design == "ziginex":     # its closest existing model is the hybrid of a recurrence, latent attention and routed experts
+        others.insert(0, ("sarizen", _sarizen_shape(width, layers, heads, experts, top, expert_ff, shared_ff, rank, window, vocab)))
     for name, cfg in [(design, raw)] + others:
         config = config_from_dict(cfg)
         engine = Engine.from_config(config, seed=0, dtype="bfloat16", page_tokens=16,

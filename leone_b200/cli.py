@@ -289,7 +289,7 @@ def build_parser() -> argparse.ArgumentParser:
     b.add_argument("--workload", choices=["decode", "serving"], default="decode",
                    help="decode: device-timed decode and prefill; serving: many requests through the scheduler")
     b.add_argument("--requests", type=int, default=64)
-    b.add_argument("--design", choices=["sarizen", "malapel", "sakinex"], default=None,
+    b.add_argument("--design", choices=["sarizen", "malapel", "sakinex", "ziginex"], default=None,
                    help="another design at real layer sizes beside the dense decoder at equal size")
     b.add_argument("--size", choices=["small", "medium"], default="small")
     b.add_argument("--new-tokens", type=int, default=128)

@@ -38,7 +38,7 @@ MODULES: Dict[str, List[str]] = {
     # delta rule
     "mixers": ["linear_attention.cu", "attention_latent.cu", "attention_latent_mma.cu", "attention_masked.cu",
                "attention_masked_mma.cu", "experts.cu", "norm_act.cu", "short_conv.cu", "attention_pooled.cu",
-               "attention_mixed_heads.cu", "gated_delta.cu"],
+               "attention_mixed_heads.cu", "attention_mixed_heads_mma.cu", "gated_delta.cu"],
     # the entry point that allocates nothing (leone_static.h); it compiles attention_tiled.cu in
     "static": ["attention_decode_static.cu"],
     # the host side of the runtime (pages, block tables, step metadata, the scheduler's decisions,

@@ -899,8 +899,10 @@ class CudaOps:
         for v, count in ((temp, n_q), (mix, n_q * n_q), (sink, n_q)):
             _need(v is None or (v.dtype == torch.float32 and v.is_contiguous() and v.numel() == count),
                   "attention_mixed_heads: per-head constants")
-        # steps of few tokens: a token's key tiles are dealt to several blocks
         size = int(mask_size or 0)
+        if self.attention_mixed_heads_tiled(ctx, q, out, cache, n_q, n_kv, dk, dv, scale, temp, cap, mix, sink, mask, size):
+            return
+        # steps of few tokens: a token's key tiles are dealt to several blocks
         keys = min(size, ctx.max_ctx_len) if mask != "causal" and size else ctx.max_ctx_len
         splits = max(1, min(32, -(-keys // 32), 296 // max(n, 1)))
         partial = None
@@ -913,6 +915,33 @@ class CudaOps:
             bt.shape[1], _ptr(ctx.seq_of_token), _ptr(ctx.positions), n, n_q, n_kv, dk, dv, c_float(scale), _ptr(temp),
             c_float(cap or 0.0), _ptr(mix), _ptr(sink), self._MASKS[mask], size, cache.page_tokens, kp.shape[0],
             bt.shape[0], splits, _ptr(ctx.status), self._stream()), "attention_mixed_heads")
+
+    def attention_mixed_heads_tiled(self, ctx, q, out, cache, n_q, n_kv, dk, dv, scale, temp, cap, mix, sink, mask, size) -> bool:
+        """The tensor-core form of :meth:`attention_mixed_heads` (``csrc/attention_mixed_heads_mma.cu``) for
+        prompt portions in bfloat16 where the sizes allow; False if it does not apply.  The step's rows are
+        cut into tiles of 16 consecutive rows of one sequence (the cut is the same for every layer)."""
+        if (q.dtype != torch.bfloat16 or ctx.decode_only or ctx.max_q_len < 8 or q.stride(0) % 8 or q.data_ptr() % 16
+                or os.environ.get("LEONE_NO_MIXED_MMA", "0") == "1"):
+            return False
+        groups, smem = c_int(0), c_int(0)
+        if not self.mixers.leone_attention_mixed_heads_mma_plan(n_q, n_kv, dk, dv, ctypes.byref(groups), ctypes.byref(smem)):
+            return False
+        tiles = ctx.__dict__.get("_row_tiles")
+        if tiles is None:
+            rows, at = [], 0
+            for s, n in enumerate(ctx.q_lens):
+                for r0 in range(0, int(n), 16):
+                    rows += [s, at + r0, min(16, int(n) - r0)]
+                at += int(n)
+            tiles = ctx.__dict__["_row_tiles"] = (len(rows) // 3, torch.tensor(rows, dtype=torch.int32).to(self.device))
+        kp, vp, bt = cache.k_pool, cache.v_pool, cache.block_table
+        self.launches += 1
+        _check(self.mixers.leone_attention_mixed_heads_mma(
+            _ptr(q), q.stride(0), _ptr(out), out.stride(0), _ptr(kp), _ptr(vp), _ptr(bt), bt.shape[1], _ptr(ctx.positions),
+            _ptr(tiles[1]), tiles[0], n_q, n_kv, dk, dv, c_float(scale), _ptr(temp), c_float(cap or 0.0), _ptr(mix),
+            _ptr(sink), self._MASKS[mask], size, cache.page_tokens, kp.shape[0], bt.shape[0], _ptr(ctx.status),
+            self._stream()), "attention_mixed_heads_mma")
+        return True
 
     def gated_delta(self, ctx, act, raw, out, state, a_log, dt_bias, heads, kv_heads, dim, vdim, q_off, k_off, v_off,
                     a_off, b_off, q_scale):

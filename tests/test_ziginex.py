@@ -284,7 +284,7 @@ def test_bfloat16_replay_without_routers_row_by_row(which, mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("switch", ["LEONE_NO_LATENT_MMA", "LEONE_NO_TENSOR_CORES"])
+@pytest.mark.parametrize("switch", ["LEONE_NO_LATENT_MMA", "LEONE_NO_TENSOR_CORES", "LEONE_NO_MIXED_MMA"])
 @pytest.mark.parametrize("which", ["C", "D"])
 def test_bfloat16_kernel_switches(which, switch, monkeypatch):
     """With a bfloat16 kernel's switch thrown its any-size form runs, and the same traces still agree
