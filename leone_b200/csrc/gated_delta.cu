@@ -15,7 +15,8 @@
 //
 // A block owns (sequence, head, a slice of value columns).  A value column's rows are dealt to P
 // lanes (row i belongs to lane part i % P), DPT rows each in registers; the two sums over rows of a
-// token are P-lane shuffles, so a token costs no block-wide barrier.  Tokens are staged 16 at a time.
+// token are P-lane shuffles, so a token costs no block-wide barrier.  Tokens are staged 16 at a time, the
+// next 16 requested while the current ones are walked.
 //
 // Then `group_gate_norm`: every head's output is divided by its root mean square over vdim,
 // multiplied by a weight [vdim] shared by the heads and by act(gate), and stored in the run dtype.
@@ -46,11 +47,7 @@ gated_delta_kernel(const float* __restrict__ act, int lda, int q_off, int k_off,
   constexpr int CW = 32 / P;                    // value columns per warp
   constexpr int COLS = CW * (kDeltaThreads / 32);
   extern __shared__ __align__(16) float smem[];
-  float* q_s = smem;                            // [tokens][DIMP]
-  float* k_s = q_s + kDeltaTokens * DIMP;       // [tokens][DIMP]
-  float* v_s = k_s + kDeltaTokens * DIMP;       // [tokens][COLS]
-  float* g_s = v_s + kDeltaTokens * COLS;       // [tokens]
-  float* b_s = g_s + kDeltaTokens;              // [tokens]
+  // two stages of: q [tokens][DIMP], k [tokens][DIMP], v [tokens][COLS], decay [tokens], beta [tokens]
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int part = lane % P;
   const int col_local = warp * CW + lane / P;
@@ -73,66 +70,104 @@ gated_delta_kernel(const float* __restrict__ act, int lda, int q_off, int k_off,
     S[r] = (i < dim && col < vdim) ? st[(size_t)i * vdim + col] : 0.f;
   }
   const float rate = expf(a_log[h]), bias = dt_bias[h];
-  for (int tb = t0; tb < t1; tb += kDeltaTokens) {
+  // The raw rows of the next 16 tokens are requested (cp.async, 4 bytes each: no alignment is asked of the
+  // rows) before the current 16 are walked, so the walk hides their latency; stage = which half of the
+  // doubled buffers holds the current tokens.
+  constexpr int kStage = kDeltaTokens * (2 * DIMP + COLS) + 2 * kDeltaTokens;
+  auto request = [&](int tb, int stage) {
     const int nt = min(kDeltaTokens, t1 - tb);
-    __syncthreads();
+    float* qd = smem + stage * kStage;
+    float* kd = qd + kDeltaTokens * DIMP;
+    float* vd = kd + kDeltaTokens * DIMP;
     for (int i = tid; i < nt * DIMP; i += kDeltaThreads) {
       const int tt = i / DIMP, d = i - tt * DIMP;
-      const float* row = act + (size_t)(tb + tt) * lda + (size_t)kvh * dim + d;
-      q_s[i] = d < dim ? row[q_off] : 0.f;
-      k_s[i] = d < dim ? row[k_off] : 0.f;
+      if (d < dim) {
+        const float* row = act + (size_t)(tb + tt) * lda + (size_t)kvh * dim + d;
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(qd + i)), "l"(row + q_off));
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(kd + i)), "l"(row + k_off));
+      } else {
+        qd[i] = 0.f;
+        kd[i] = 0.f;
+      }
     }
     for (int i = tid; i < nt * COLS; i += kDeltaThreads) {
       const int tt = i / COLS, c = i - tt * COLS;
-      v_s[i] = v0 + c < vdim ? act[(size_t)(tb + tt) * lda + v_off + (size_t)h * vdim + v0 + c] : 0.f;
+      if (v0 + c < vdim)
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(vd + i)),
+                     "l"(act + (size_t)(tb + tt) * lda + v_off + (size_t)h * vdim + v0 + c));
+      else vd[i] = 0.f;
     }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  // gates of the tokens and unit vectors, in place, once the rows have landed
+  auto finish = [&](int tb, int stage) {
+    const int nt = min(kDeltaTokens, t1 - tb);
+    float* qd = smem + stage * kStage;
+    float* kd = qd + kDeltaTokens * DIMP;
+    float* gd = kd + kDeltaTokens * DIMP + kDeltaTokens * COLS;
     if (tid < nt) {
       const float* row = raw + (size_t)(tb + tid) * ldr;
       const float z = row[a_off + h] + bias;
       const float sp = z > 20.f ? z : log1pf(expf(z));           // softplus
-      g_s[tid] = expf(-rate * sp);
-      b_s[tid] = 1.f / (1.f + expf(-row[b_off + h]));
+      gd[tid] = expf(-rate * sp);
+      gd[kDeltaTokens + tid] = 1.f / (1.f + expf(-row[b_off + h]));
     }
-    __syncthreads();
-    // unit vectors: a warp takes every fourth token
     for (int tt = warp; tt < nt; tt += kDeltaThreads / 32) {
       float sq = 0.f, sk = 0.f;
       for (int d = lane; d < dim; d += 32) {
-        sq = fmaf(q_s[tt * DIMP + d], q_s[tt * DIMP + d], sq);
-        sk = fmaf(k_s[tt * DIMP + d], k_s[tt * DIMP + d], sk);
+        sq = fmaf(qd[tt * DIMP + d], qd[tt * DIMP + d], sq);
+        sk = fmaf(kd[tt * DIMP + d], kd[tt * DIMP + d], sk);
       }
       sq = warp_sum(sq);
       sk = warp_sum(sk);
       const float rq = q_scale / sqrtf(sq + 1e-6f), rk = 1.f / sqrtf(sk + 1e-6f);
       for (int d = lane; d < dim; d += 32) {
-        q_s[tt * DIMP + d] *= rq;
-        k_s[tt * DIMP + d] *= rk;
+        qd[tt * DIMP + d] *= rq;
+        kd[tt * DIMP + d] *= rk;
       }
     }
-    __syncthreads();
+  };
+  request(t0, 0);
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncthreads();
+  finish(t0, 0);
+  __syncthreads();
+  int stage = 0;
+  for (int tb = t0; tb < t1; tb += kDeltaTokens, stage ^= 1) {
+    const int nt = min(kDeltaTokens, t1 - tb);
+    const bool more = tb + kDeltaTokens < t1;
+    if (more) request(tb + kDeltaTokens, stage ^ 1);
+    const float* q_c = smem + stage * kStage;
+    const float* k_c = q_c + kDeltaTokens * DIMP;
+    const float* v_c = k_c + kDeltaTokens * DIMP;
+    const float* g_c = v_c + kDeltaTokens * COLS;
     for (int tt = 0; tt < nt; ++tt) {
-      const float g = g_s[tt], beta = b_s[tt], vj = v_s[tt * COLS + col_local];
-      const float* kk = k_s + tt * DIMP + part;
-      const float* qq = q_s + tt * DIMP + part;
+      const float g = g_c[tt], beta = g_c[kDeltaTokens + tt], vj = v_c[tt * COLS + col_local];
+      const float* kk = k_c + tt * DIMP + part;
+      const float* qq = q_c + tt * DIMP + part;
       float kv[DPT];
-      float r0 = 0.f, r1 = 0.f;
+      float r4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < DPT; ++r) {
         kv[r] = kk[P * r];
-        if (r & 1) r1 = fmaf(S[r], kv[r], r1);
-        else r0 = fmaf(S[r], kv[r], r0);
+        r4[r & 3] = fmaf(S[r], kv[r], r4[r & 3]);
       }
-      const float dot = part_sum<P>(r0 + r1);
+      const float dot = part_sum<P>((r4[0] + r4[1]) + (r4[2] + r4[3]));
       const float u = beta * (vj - g * dot);
-      float o0 = 0.f, o1 = 0.f;
+      float o4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int r = 0; r < DPT; ++r) {
         S[r] = fmaf(g, S[r], kv[r] * u);
-        if (r & 1) o1 = fmaf(S[r], qq[P * r], o1);
-        else o0 = fmaf(S[r], qq[P * r], o0);
+        o4[r & 3] = fmaf(S[r], qq[P * r], o4[r & 3]);
       }
-      const float o = part_sum<P>(o0 + o1);
+      const float o = part_sum<P>((o4[0] + o4[1]) + (o4[2] + o4[3]));
       if (part == 0 && col < vdim) out[(size_t)(tb + tt) * ldo + (size_t)h * vdim + col] = o;
+    }
+    if (more) {
+      asm volatile("cp.async.wait_group 0;" ::: "memory");
+      __syncthreads();
+      finish(tb + kDeltaTokens, stage ^ 1);
+      __syncthreads();
     }
   }
   if (col < vdim) {
@@ -189,7 +224,7 @@ extern "C" int leone_gated_delta(const float* act, int lda, int q_off, int k_off
 #define DELTA(DPT, P)                                                                                                 \
   {                                                                                                                   \
     constexpr int cols = (32 / P) * (kDeltaThreads / 32);                                                             \
-    const size_t smem = sizeof(float) * (size_t)(kDeltaTokens * (2 * DPT * P + cols) + 2 * kDeltaTokens);             \
+    const size_t smem = 2 * sizeof(float) * (size_t)(kDeltaTokens * (2 * DPT * P + cols) + 2 * kDeltaTokens);             \
     static bool configured = false;                                                                                   \
     if (!configured && smem > 48 * 1024) {                                                                            \
       cudaFuncSetAttribute(gated_delta_kernel<DPT, P>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
@@ -200,11 +235,14 @@ extern "C" int leone_gated_delta(const float* act, int lda, int q_off, int k_off
                          a_log, dt_bias, q_scale, out, ldo, state, q_start, slot_ids, heads, kv_heads, dim, vdim,     \
                          n_slots, status);                                                                            \
   }
+  // rows dealt to 16 lanes from 33 rows on: a token's cost is the latency of its chain of sums and shuffles,
+  // not its multiply-adds (dim 128: 0.48 us a token with 16 lanes a column, 0.59 with 4), and two columns a warp
+  // give a prompt of one sequence 8 blocks a head
   if (dim <= 16) DELTA(4, 4)
   if (dim <= 32) DELTA(8, 4)
-  if (dim <= 64) DELTA(16, 4)
-  if (dim <= 128) DELTA(32, 4)
-  if (dim <= 256) DELTA(64, 4)
+  if (dim <= 64) DELTA(4, 16)
+  if (dim <= 128) DELTA(8, 16)
+  if (dim <= 256) DELTA(16, 16)
   DELTA(16, 32)
 #undef DELTA
 }
