@@ -33,6 +33,39 @@ template <typename T> __host__ __device__ inline int padded_row(int d) {
   return e;
 }
 
+// Rows j0 .. j0 + nt - 1 of every key/value head from the pages into shared memory ([head][kt][pitch] elements):
+// 16 bytes a load where the rows allow it (the shared rows are only 4-byte aligned, so four stores), else
+// element by element.  A key without a valid page is a row of zeros.
+template <typename T>
+__device__ __forceinline__ void copy_tile(T* dst, int pitch, const T* __restrict__ pool, int d, const int* page_s, int j0,
+                                          int nt, int n_kv, int kt, int page_tokens, int tid) {
+  constexpr int V = 16 / (int)sizeof(T);
+  if (d % V == 0 && (pitch * (int)sizeof(T)) % 4 == 0 && (((uintptr_t)pool) & 15) == 0) {
+    const int chunks = d / V;
+    for (int i = tid; i < n_kv * nt * chunks; i += kMixThreads) {
+      const int c = i % chunks, row = i / chunks;
+      const int j = row % nt, g = row / nt;
+      const int page = page_s[j];
+      uint4 val = make_uint4(0, 0, 0, 0);
+      if (page >= 0)
+        val = *reinterpret_cast<const uint4*>(pool + (((size_t)page * n_kv + g) * page_tokens + (j0 + j) % page_tokens) * d + c * V);
+      uint32_t* out = reinterpret_cast<uint32_t*>(dst + ((size_t)g * kt + j) * pitch + c * V);
+      out[0] = val.x;
+      out[1] = val.y;
+      out[2] = val.z;
+      out[3] = val.w;
+    }
+    return;
+  }
+  for (int i = tid; i < n_kv * nt * d; i += kMixThreads) {
+    const int e = i % d, row = i / d;
+    const int j = row % nt, g = row / nt;
+    const int page = page_s[j];
+    dst[((size_t)g * kt + j) * pitch + e] =
+        page < 0 ? from_float<T>(0.f) : pool[(((size_t)page * n_kv + g) * page_tokens + (j0 + j) % page_tokens) * d + e];
+  }
+}
+
 // mask: 0 causal, 1 window, 2 chunk
 template <typename T, int R>
 __global__ void __launch_bounds__(kMixThreads)
@@ -95,22 +128,8 @@ attention_mixed_heads_kernel(const T* __restrict__ q, int ldq, T* __restrict__ o
       page_s[tid] = (page < 0 || page >= n_pages) ? -1 : page;
     }
     __syncthreads();
-    for (int i = tid; i < n_kv * nt * dk; i += kMixThreads) {
-      const int d = i % dk, row = i / dk;
-      const int j = row % nt, g = row / nt;
-      const int page = page_s[j];
-      k_s[((size_t)g * kt + j) * dkp + d] =
-          page < 0 ? from_float<T>(0.f)
-                   : k_pool[(((size_t)page * n_kv + g) * page_tokens + (j0 + j) % page_tokens) * dk + d];
-    }
-    for (int i = tid; i < n_kv * nt * dv; i += kMixThreads) {
-      const int d = i % dv, row = i / dv;
-      const int j = row % nt, g = row / nt;
-      const int page = page_s[j];
-      v_s[((size_t)g * kt + j) * dv + d] =
-          page < 0 ? from_float<T>(0.f)
-                   : v_pool[(((size_t)page * n_kv + g) * page_tokens + (j0 + j) % page_tokens) * dv + d];
-    }
+    copy_tile<T>(k_s, dkp, k_pool, dk, page_s, j0, nt, n_kv, kt, page_tokens, tid);
+    copy_tile<T>(v_s, dv, v_pool, dv, page_s, j0, nt, n_kv, kt, page_tokens, tid);
     __syncthreads();
     for (int i = tid; i < n_q * kt; i += kMixThreads) {
       const int h = i / kt, j = i - h * kt;

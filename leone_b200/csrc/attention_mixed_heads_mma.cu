@@ -8,14 +8,17 @@
 //   (2) the heads are dealt to the warps; a warp forms raw = Q_h K^T for its heads with mma.sync (Q
 //       fragments from shared memory, fp32 sums), multiplies by scale * temp_h, applies the soft cap and
 //       leaves the 16 x 32 raw scores in shared memory;
-//   (3) every thread owns one (row, key) pair and mixes: s_h = sum_g M[h, g] raw_g for the heads of the
-//       block's head group, fp32 on CUDA cores, and applies the mask (-inf);
+//   (3) every thread owns one (row, key) pair, takes the raw scores of all heads into registers and mixes:
+//       s_h = sum_g M[h, g] raw_g for the heads of the block's head group, fp32 on CUDA cores, applies the
+//       mask (-inf) and writes the mixed scores over the raw ones of those heads;
 //   (4) a warp takes the mixed scores of its head in accumulator layout, keeps the running maximum and
 //       sum (started at (sink, 1)), and adds P V with mma.sync.  The weights stay fp32: P is split into
 //       two bfloat16 terms (P = hi + lo, two MMAs), so that the product sees 16 bits of it.
 // Outputs of one head fill 64 registers of a thread at value width 128, so a block accumulates at most
 // 16 heads x 128 columns; with more, several blocks share a query tile: each forms all raw scores and
-// mixes, normalises and accumulates the heads of its group only.
+// mixes, normalises and accumulates the heads of its group only.  Where the query tile of all heads does not
+// fit beside the key, value and score tiles (32 heads of 128), its fragments are read from global memory
+// (the L2) for every key tile instead of from shared memory (QS = false).  At most 32 query heads.
 #include "common.cuh"
 #include "mma_tile.cuh"
 
@@ -23,6 +26,7 @@ namespace leone {
 
 constexpr int kMmThreads = 512, kMmWarps = 16, kMmRows = 16, kMmKeys = 32;
 constexpr int kRawPitch = kMmKeys + 1;      // floats per row of a head's score tile
+constexpr int kMmMaxHeads = 32;             // raw scores of one (row, key) pair a thread holds while it mixes
 
 __device__ __forceinline__ void ldsm4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
@@ -55,8 +59,9 @@ struct MixedMmaArgs {
   int* status;
 };
 
-// DV16: value width / 16.  HPW: heads of the group a warp accumulates.
-template <int DV16, int HPW>
+// DV16: value width / 16.  HPW: heads of the group a warp accumulates.  QS: the query tile is in shared memory.
+// MH: 16 or 32, at least the number of query heads (the raw scores a thread holds while it mixes).
+template <int DV16, int HPW, bool QS, int MH>
 __global__ void __launch_bounds__(kMmThreads, 1)
 attention_mixed_heads_mma_kernel(MixedMmaArgs a) {
   pdl_trigger();
@@ -67,12 +72,11 @@ attention_mixed_heads_mma_kernel(MixedMmaArgs a) {
   const int n_q = a.n_q, n_kv = a.n_kv, dk = a.dk, dv = DV16 * 16;
   const int hg0 = blockIdx.y * a.group_heads, hg1 = min(n_q, hg0 + a.group_heads);
   const int q_pitch = n_q * dk * 2 + 16, k_pitch = dk * 2 + 16, v_pitch = dv * 2 + 16;      // bytes
-  unsigned char* q_s = smem;                                             // [16][n_q * dk]
-  unsigned char* k_s = q_s + (size_t)kMmRows * q_pitch;                  // [n_kv][32][dk]
+  unsigned char* q_s = smem;                                             // [16][n_q * dk] (QS only)
+  unsigned char* k_s = q_s + (QS ? (size_t)kMmRows * q_pitch : 0);       // [n_kv][32][dk]
   unsigned char* v_s = k_s + (size_t)n_kv * kMmKeys * k_pitch;           // [n_kv][32][dv]
   float* raw_s = reinterpret_cast<float*>(v_s + (size_t)n_kv * kMmKeys * v_pitch);      // [n_q][16][33]
-  float* mixed_s = raw_s + (size_t)n_q * kMmRows * kRawPitch;            // [group_heads][16][33]
-  float* mix_s = mixed_s + (size_t)a.group_heads * kMmRows * kRawPitch;  // [group_heads][n_q4], rows 16-byte aligned
+  float* mix_s = raw_s + (size_t)n_q * kMmRows * kRawPitch;              // [group_heads][n_q4], rows 16-byte aligned
   int* page_s = reinterpret_cast<int*>(mix_s + (size_t)a.group_heads * ((n_q + 3) / 4 * 4));      // [32]
   const int n_q4 = (n_q + 3) / 4 * 4;
   if (seq < 0 || seq >= a.n_seqs || n_rows <= 0) return;
@@ -85,7 +89,7 @@ attention_mixed_heads_mma_kernel(MixedMmaArgs a) {
   const int* table = a.block_table + (size_t)seq * a.bt_width;
   // Q tile (rows past the tile are zeros) and the group's rows of the mixing matrix
   {
-    const int chunks = n_q * dk / 8;
+    const int chunks = QS ? n_q * dk / 8 : 0;
     for (int i = tid; i < kMmRows * chunks; i += kMmThreads) {
       const int r = i / chunks, c = i - r * chunks;
       const bool ok = r < n_rows;
@@ -164,9 +168,20 @@ attention_mixed_heads_mma_kernel(MixedMmaArgs a) {
 #pragma unroll
         for (int i = 0; i < 4; ++i) s[n][i] = 0.f;
       const uint32_t qh = q_base + (uint32_t)(h * dk * 2), kg = k_base + (uint32_t)((h / group) * kMmKeys * k_pitch);
+      // without the query tile in shared memory: this lane's elements of the A fragments, rows g and g + 8
+      const __nv_bfloat16* qg0 = a.q + (size_t)(row0 + (lane >> 2)) * a.ldq + (size_t)h * dk + 2 * (lane & 3);
+      const __nv_bfloat16* qg1 = qg0 + (size_t)8 * a.ldq;
+      const bool ok0 = (lane >> 2) < n_rows, ok1 = (lane >> 2) + 8 < n_rows;
       for (int ks = 0; ks < dk / 16; ++ks) {
         uint32_t a0, a1, a2, a3;
-        ldsm4(qh + (lane & 15) * q_pitch + (lane >> 4) * 16 + ks * 32, a0, a1, a2, a3);
+        if (QS) {
+          ldsm4(qh + (lane & 15) * q_pitch + (lane >> 4) * 16 + ks * 32, a0, a1, a2, a3);
+        } else {
+          a0 = ok0 ? __ldg(reinterpret_cast<const uint32_t*>(qg0 + ks * 16)) : 0u;
+          a1 = ok1 ? __ldg(reinterpret_cast<const uint32_t*>(qg1 + ks * 16)) : 0u;
+          a2 = ok0 ? __ldg(reinterpret_cast<const uint32_t*>(qg0 + ks * 16 + 8)) : 0u;
+          a3 = ok1 ? __ldg(reinterpret_cast<const uint32_t*>(qg1 + ks * 16 + 8)) : 0u;
+        }
 #pragma unroll
         for (int np = 0; np < 2; ++np) {
           uint32_t b0, b1, b2, b3;
@@ -194,22 +209,27 @@ attention_mixed_heads_mma_kernel(MixedMmaArgs a) {
       bool seen = r < n_rows && key <= p;
       if (a.mask == 1) seen = seen && p - key < a.mask_size;
       else if (a.mask == 2) seen = seen && key / a.mask_size == p / a.mask_size;
-      const float* src = raw_s + r * kRawPitch + j;
+      float* src = raw_s + r * kRawPitch + j;
+      float rv[MH];
+#pragma unroll
+      for (int g = 0; g < MH; ++g) rv[g] = g < n_q ? src[(size_t)g * kMmRows * kRawPitch] : 0.f;
       for (int h = 0; h < hg1 - hg0; ++h) {
         float v = -INFINITY;
         if (seen) {
           v = 0.f;
           const float4* row = reinterpret_cast<const float4*>(mix_s + h * n_q4);
-          for (int g4 = 0; g4 < n_q4 / 4; ++g4) {
-            const float4 w = row[g4];
-            const int g = g4 * 4;
-            v = fmaf(w.x, src[(size_t)g * kMmRows * kRawPitch], v);
-            if (g + 1 < n_q) v = fmaf(w.y, src[(size_t)(g + 1) * kMmRows * kRawPitch], v);
-            if (g + 2 < n_q) v = fmaf(w.z, src[(size_t)(g + 2) * kMmRows * kRawPitch], v);
-            if (g + 3 < n_q) v = fmaf(w.w, src[(size_t)(g + 3) * kMmRows * kRawPitch], v);
+#pragma unroll
+          for (int g4 = 0; g4 < MH / 4; ++g4) {
+            if (g4 * 4 < n_q) {
+              const float4 w = row[g4];          // the matrix's row is padded with zeros
+              v = fmaf(w.x, rv[g4 * 4], v);
+              v = fmaf(w.y, rv[g4 * 4 + 1], v);
+              v = fmaf(w.z, rv[g4 * 4 + 2], v);
+              v = fmaf(w.w, rv[g4 * 4 + 3], v);
+            }
           }
         }
-        mixed_s[((size_t)h * kMmRows + r) * kRawPitch + j] = v;
+        src[(size_t)(hg0 + h) * kMmRows * kRawPitch] = v;      // over the raw score of that head: this thread alone reads this pair
       }
     }
     __syncthreads();
@@ -218,7 +238,7 @@ attention_mixed_heads_mma_kernel(MixedMmaArgs a) {
     for (int u = 0; u < HPW; ++u) {
       const int hl = warp + kMmWarps * u;
       if (hg0 + hl >= hg1) continue;
-      const float* src = mixed_s + (size_t)hl * kMmRows * kRawPitch;
+      const float* src = raw_s + (size_t)(hg0 + hl) * kMmRows * kRawPitch;
       float s[4][4];
       float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
@@ -304,16 +324,19 @@ using namespace leone;
 
 // 1 if the tensor-core form takes these sizes; *groups: blocks that share a query tile, *smem: bytes a block needs
 extern "C" int leone_attention_mixed_heads_mma_plan(int n_q, int n_kv, int dk, int dv, int* groups, int* smem) {
-  if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0 || dk % 16 != 0 || dk <= 0 || (dv != 32 && dv != 64 && dv != 96 && dv != 128))
+  if (n_q <= 0 || n_q > kMmMaxHeads || n_kv <= 0 || n_q % n_kv != 0 || dk % 16 != 0 || dk <= 0 ||
+      (dv != 32 && dv != 64 && dv != 96 && dv != 128))
     return 0;
   int hg = 1;
   while (((n_q + hg - 1) / hg + kMmWarps - 1) / kMmWarps * dv > 128) ++hg;
   const int gh = (n_q + hg - 1) / hg;
-  const long long bytes = (long long)kMmRows * (n_q * dk * 2 + 16) + (long long)n_kv * kMmKeys * (dk * 2 + 16 + dv * 2 + 16) +
-                          4LL * (n_q + gh) * kMmRows * kRawPitch + 4LL * gh * ((n_q + 3) / 4 * 4) + 4 * kMmKeys;
-  if (bytes > 220 * 1024) return 0;
+  const long long q_bytes = (long long)kMmRows * (n_q * dk * 2 + 16);
+  const long long rest = (long long)n_kv * kMmKeys * (dk * 2 + 16 + dv * 2 + 16) + 4LL * n_q * kMmRows * kRawPitch +
+                         4LL * gh * ((n_q + 3) / 4 * 4) + 4 * kMmKeys;
+  if (rest > 220 * 1024) return 0;
   *groups = hg;
-  *smem = (int)bytes;
+  // negative: without the query tile (its fragments come from global memory)
+  *smem = q_bytes + rest <= 220 * 1024 ? (int)(q_bytes + rest) : -(int)rest;
   return 1;
 }
 
@@ -336,15 +359,25 @@ extern "C" int leone_attention_mixed_heads_mma(const void* q, int ldq, void* out
                  (const __nv_bfloat16*)v_pool, block_table, bt_width, positions, tiles, n_q, n_kv, dk, dv, scale, temp,
                  cap, mix, sink, mask, mask_size, page_tokens, n_pages, n_seqs, gh, status};
   const int hpw = (gh + kMmWarps - 1) / kMmWarps;
-#define MM(DV16, HPW)                                                                                                \
+  const bool q_in_smem = smem > 0;
+  if (!q_in_smem) smem = -smem;
+#define MM1(DV16, HPW, QS, MH)                                                                                       \
   {                                                                                                                  \
     static int configured = 0;                                                                                       \
     if (smem > configured) {                                                                                         \
-      cudaFuncSetAttribute(attention_mixed_heads_mma_kernel<DV16, HPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem); \
+      cudaFuncSetAttribute(attention_mixed_heads_mma_kernel<DV16, HPW, QS, MH>,                                      \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, smem);                                       \
       configured = smem;                                                                                             \
     }                                                                                                                \
-    return launch_kernel(attention_mixed_heads_mma_kernel<DV16, HPW>, dim3(n_tiles, groups), dim3(kMmThreads),       \
-                         (size_t)smem, stream, a);                                                                   \
+    return launch_kernel(attention_mixed_heads_mma_kernel<DV16, HPW, QS, MH>, dim3(n_tiles, groups),                 \
+                         dim3(kMmThreads), (size_t)smem, stream, a);                                                 \
+  }
+#define MM(DV16, HPW)                                                                                                \
+  {                                                                                                                  \
+    if (q_in_smem && n_q <= 16) MM1(DV16, HPW, true, 16)                                                             \
+    if (q_in_smem) MM1(DV16, HPW, true, 32)                                                                          \
+    if (n_q <= 16) MM1(DV16, HPW, false, 16)                                                                         \
+    MM1(DV16, HPW, false, 32)                                                                                        \
   }
   if (dv == 128 && hpw == 1) MM(8, 1)
   if (dv == 96 && hpw == 1) MM(6, 1)
@@ -354,5 +387,6 @@ extern "C" int leone_attention_mixed_heads_mma(const void* q, int ldq, void* out
   if (dv == 32 && hpw == 2) MM(2, 2)
   if (dv == 32 && hpw <= 4) MM(2, 4)
 #undef MM
+#undef MM1
   return kRefusedSize;
 }

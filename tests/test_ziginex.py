@@ -542,7 +542,10 @@ def _mixed_scores_attention(q, k, v, scale, temp, cap, mix, sink, mask, size):
     (6, 2, 12, 20, "chunk", 9, 8, "tcms"), (4, 4, 24, 16, "chunk", 70, 16, "tms"), (3, 1, 40, 8, "chunk", 1, 4, "cs"),
     (2, 1, 16, 136, "causal", 0, 16, "tcm"), (8, 2, 128, 128, "chunk", 64, 16, "tcms"), (16, 4, 96, 96, "window", 17, 16, "ms"),
     (5, 5, 16, 16, "chunk", 400, 16, "t"), (32, 8, 64, 64, "chunk", 128, 32, "tcms"), (1, 1, 7, 5, "chunk", 33, 16, "cms"),
-    (7, 7, 9, 3, "causal", 0, 8, "")])
+    (7, 7, 9, 3, "causal", 0, 8, ""),
+    # the tensor-core form's other shapes: two blocks a query tile with the query tile left in global memory, two
+    # heads a warp, value width 96 on a key width of 48
+    (32, 8, 128, 128, "chunk", 100, 16, "tcms"), (32, 4, 32, 32, "causal", 0, 16, "ms"), (8, 2, 48, 96, "window", 50, 16, "tcms")])
 def test_mixed_heads_attention_kernel_against_the_plain_rule(n_q, n_kv, dk, dv, mask, size, page, parts):
     """The attention kernel alone over shuffled pages: three sequences of unequal lengths as prompt
     portions that start in the middle of a sequence, and as a decode step (where a token's keys are split
