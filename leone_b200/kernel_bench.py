@@ -358,6 +358,61 @@ def bench_conv_and_gru(ops, tokens, batch, width, taps, chunk, reps, warmup):
     return result
 
 
+def bench_mixed_attention(ops, tokens, batch, context, n_q, n_kv, dk, dv, mask, size, page_tokens, reps, warmup):
+    """Attention with scores mixed across heads (``CudaOps.attention_mixed_heads``, with temperature, cap,
+    mixing matrix and sink): one prompt of ``tokens`` tokens, or with ``batch`` a decode step of that many
+    sequences at ``context`` keys."""
+    decode = batch > 0
+    seqs, length = (batch, context) if decode else (1, tokens)
+    blocks = -(-length // page_tokens)
+    k_pool = torch.randn((seqs * blocks, n_kv, page_tokens, dk), device=DEV).to(torch.bfloat16)
+    v_pool = torch.randn((seqs * blocks, n_kv, page_tokens, dv), device=DEV).to(torch.bfloat16)
+    table = torch.randperm(seqs * blocks, device=DEV).to(torch.int32).view(seqs, blocks)
+    ctx = _step_of(seqs, 1 if decode else tokens, length)
+    n = ctx.n_tokens
+    qkv = torch.randn((n, (n_q + n_kv) * dk + n_kv * dv), device=DEV).to(torch.bfloat16)
+    out = torch.empty((n, n_q * dv), device=DEV, dtype=torch.bfloat16)
+    cache = types.SimpleNamespace(k_pool=k_pool, v_pool=v_pool, block_table=table, page_tokens=page_tokens)
+    temp = torch.ones(n_q, device=DEV)
+    mix = torch.eye(n_q, device=DEV) + 0.1 * torch.randn(n_q, n_q, device=DEV)
+    sink = torch.zeros(n_q, device=DEV)
+    ms = _time(lambda: ops.attention_mixed_heads(ctx, qkv, out, cache, n_q, n_kv, dk, dv, dk ** -0.5, temp, 30.0, mix, sink,
+                                                 mask, size), reps, warmup, per_graph=16 if decode else 1)
+
+    def seen(p):
+        return p + 1 if mask == "causal" else (min(p + 1, size) if mask == "window" else p % size + 1)
+    keys = seqs * seen(length - 1) if decode else sum(seen(p) for p in range(tokens))
+    row = dict(kernel="attention_mixed_heads", mask=mask, size=size, heads=n_q, kv_heads=n_kv, dk=dk, dv=dv, us=ms * 1e3)
+    if decode:
+        row.update(batch=batch, context=context, gbs=keys * n_kv * (dk + dv) * 2.0 / ms / 1e6)
+    else:
+        row.update(tokens=tokens, tflops=2.0 * n_q * (dk + dv) * keys / ms / 1e9)
+    return row
+
+
+def bench_gated_delta(ops, tokens, batch, heads, kv_heads, dim, vdim, reps, warmup):
+    """The gated delta rule's recurrence (``CudaOps.gated_delta``): one prompt of ``tokens`` tokens, or with
+    ``batch`` a decode step of that many sequences."""
+    decode = batch > 0
+    seqs, q_len = (batch, 1) if decode else (1, tokens)
+    ctx = _step_of(seqs, q_len, q_len)
+    n, qk, hv = ctx.n_tokens, kv_heads * dim, heads * vdim
+    act = torch.randn((n, 2 * qk + hv), device=DEV)
+    raw = torch.randn((n, 2 * heads), device=DEV)
+    out = torch.empty((n, hv), device=DEV)
+    state = torch.zeros((seqs, heads, dim, vdim), device=DEV)
+    a_log, dt_bias = torch.zeros(heads, device=DEV), torch.zeros(heads, device=DEV)
+    ms = _time(lambda: ops.gated_delta(ctx, act, raw, out, state, a_log, dt_bias, heads, kv_heads, dim, vdim, 0, qk, 2 * qk,
+                                       0, heads, dim ** -0.5), reps, warmup, per_graph=16 if decode else 1)
+    row = dict(kernel="gated_delta", heads=heads, kv_heads=kv_heads, dim=dim, vdim=vdim, us=ms * 1e3,
+               us_per_token=ms * 1e3 / q_len, fp32_tflops=6.0 * n * heads * dim * vdim / ms / 1e9)
+    if decode:
+        row.update(batch=batch, gbs=2.0 * seqs * heads * dim * vdim * 4 / ms / 1e6)
+    else:
+        row.update(tokens=tokens)
+    return row
+
+
 def bench_sampling(ops, rows, vocab, stages, reps, warmup):
     """The sampler's truncation pipeline (sort, stages, draw) on ``rows`` rows of ``vocab`` logits;
     wall time with a synchronize on both sides (the call makes dozens of small launches)."""
@@ -380,7 +435,7 @@ def bench_sampling(ops, rows, vocab, stages, reps, warmup):
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m leone_b200.kernel_bench")
     ap.add_argument("what", choices=["gemm", "decode-attention", "prefill-attention", "layer-shapes", "sampling",
-                                     "masked-attention", "pooled-attention", "conv-gru"])
+                                     "masked-attention", "pooled-attention", "conv-gru", "mixed-attention", "gated-delta"])
     ap.add_argument("--pool", type=int, default=64, help="pooled-attention: positions per pooled block")
     ap.add_argument("--taps", type=int, default=4, help="pooled-attention, conv-gru: taps of the short convolutions")
     ap.add_argument("--width", type=int, default=2048, help="conv-gru: channels")
@@ -389,7 +444,8 @@ def main(argv=None) -> int:
     ap.add_argument("--mask-size", type=int, default=1024)
     ap.add_argument("--weights", choices=["softmax", "softmax_plus_one", "sigmoid"], default="sigmoid")
     ap.add_argument("--value-dim", type=int, default=0, help="masked-attention: value width (default: the head size)")
-    ap.add_argument("--decode", action="store_true", help="masked-attention: a decode step of --batch sequences")
+    ap.add_argument("--decode", action="store_true",
+                    help="masked-attention, pooled-attention, mixed-attention, gated-delta, conv-gru: a decode step of --batch sequences")
     ap.add_argument("--stages", default="top_k=40,top_p=0.95",
                     help="sampling: truncation stages in order, e.g. top_k=40,typical=0.9")
     ap.add_argument("--vocab", type=int, default=151936)
@@ -476,6 +532,13 @@ def main(argv=None) -> int:
         rows += bench_pooled_attention(ops, args.tokens, args.batch if args.decode else 0, args.context, args.heads,
                                        args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.mask_size,
                                        args.pool, args.page_tokens, args.reps, args.warmup, args.taps)
+    elif args.what == "mixed-attention":
+        rows.append(bench_mixed_attention(ops, args.tokens, args.batch if args.decode else 0, args.context, args.heads,
+                                          args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.mask,
+                                          args.mask_size, args.page_tokens, args.reps, args.warmup))
+    elif args.what == "gated-delta":
+        rows.append(bench_gated_delta(CudaOps(DEV, torch.float32), args.tokens, args.batch if args.decode else 0, args.heads,
+                                      args.kv_heads, args.head_dim, args.value_dim or args.head_dim, args.reps, args.warmup))
     elif args.what == "conv-gru":
         from .parts.min_gru import DEFAULT_CHUNK
         rows += bench_conv_and_gru(ops, args.tokens, args.batch if args.decode else 0, args.width, args.taps,
