@@ -321,6 +321,25 @@ def test_each_layer_alone(which, index):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_no_vector_load_fits(dtype):
+    """Odd widths everywhere (model width 50, heads of 6 and 7, latents of 9 and 5, a token table of 3, experts of
+    11, a vocabulary of 101): every kernel takes its element-by-element form, in both dtypes."""
+    raw = model(101, 50, 1e-5, side=3, layers=[
+        parallel(left(3, 1, 6, 7, 0.4, chunk=11, softcap=9.0, rot_dims=4), right(3, 1, 5, 7, conv=3), moe(11, 3, 2, identity=2)),
+        latent(3, 5, 2, 7, 9, 5, 0.3, base=300.0, scaling=(3.0, 20, 4.0, 1.0), mlp=dense(13))])
+    tensors = _random(raw, 12)
+    reqs = _requests(101, [37, 5, 18, 26], seed=3)
+    steps = replay.trace_mixed(reqs, seed=4, max_live=3)
+    eng = _engine(None, tensors, dtype, "cuda:0", max_tokens=replay.max_live_tokens(steps), page=8, raw=raw)
+    out = replay.run_trace_engine(eng, steps)
+    if dtype == "float32":
+        replay.compare(steps, out, plain.PlainZiginex(raw, tensors), reqs, what="odd sizes", **FP32)
+    else:
+        _compare_bf16_with_routers(steps, out, _plain(None, tensors, True, raw=raw), reqs, "odd sizes")
+
+
+@pytest.mark.gpu
 def test_long_prompt_and_long_decode():
     """A prompt of many pages, then 150 single-token steps across pages and chunks; position 0 alone first."""
     for dtype, tol in (("float32", FP32), ("bfloat16", BF16)):
