@@ -315,24 +315,13 @@ experts_down_kernel(const T* __restrict__ act, const T* __restrict__ w_down, flo
   }
 }
 
-// Pairs whose choice is past the last expert are identity experts: pair_out = weight * x[token].
+// hidden[t, :] (+)= sum_j pair_out[t * top + j, :], j ascending; top < 0: written, not added (|top| pairs).
+// A pair whose choice is past the last expert is an identity expert and contributes weight * x[t, :] instead
+// (x null: there are none).
 template <typename T>
-__global__ void experts_identity_kernel(const T* __restrict__ x, int ldx, const int* __restrict__ chosen,
-                                        const float* __restrict__ weight, float* __restrict__ pair_out, long long pairs,
-                                        int width, int experts, int top) {
-  pdl_trigger();
-  pdl_wait();
-  for (long long p = blockIdx.x; p < pairs; p += gridDim.x) {
-    if (chosen[p] < experts) continue;
-    const float w = weight[p];
-    const T* row = x + (size_t)(p / top) * ldx;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) pair_out[(size_t)p * width + c] = w * to_float<T>(row[c]);
-  }
-}
-
-// hidden[t, :] (+)= sum_j pair_out[t * top + j, :], j ascending; top < 0: written, not added (|top| pairs)
 __global__ void experts_combine_kernel(float* __restrict__ hidden, const float* __restrict__ pair_out,
-                                       long long total, int width, int top) {
+                                       long long total, int width, int top, const T* __restrict__ x, int ldx,
+                                       const int* __restrict__ chosen, const float* __restrict__ weight, int experts) {
   pdl_trigger();      // the next kernel may be scheduled; it waits for this one before it touches data
   pdl_wait();
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -341,7 +330,11 @@ __global__ void experts_combine_kernel(float* __restrict__ hidden, const float* 
     const int c = (int)(i - t * width);
     float sum = 0.f;
     const int n = top < 0 ? -top : top;
-    for (int j = 0; j < n; ++j) sum += pair_out[((size_t)t * n + j) * width + c];
+    for (int j = 0; j < n; ++j) {
+      const size_t p = (size_t)t * n + j;
+      if (x != nullptr && chosen[p] >= experts) sum += weight[p] * to_float<T>(x[(size_t)t * ldx + c]);
+      else sum += pair_out[p * width + c];
+    }
     hidden[i] = top < 0 ? sum : hidden[i] + sum;
   }
 }
@@ -565,15 +558,6 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
   const long long pairs = (long long)n_tokens * top;
   if (pairs > (1 << 30)) return kRefusedSize;
   launch_kernel(group_pairs_kernel, dim3(1), dim3(1024), sizeof(int) * (size_t)experts, stream, chosen, (int)pairs, experts, offsets, order);
-  if (identity > 0) {
-    const unsigned iblocks = (unsigned)(pairs < 148 * 8 ? pairs : 148 * 8);
-    if (dtype == 0)
-      launch_kernel(experts_identity_kernel<float>, dim3(iblocks), dim3(128), 0, stream, (const float*)x, ldx, chosen, weight,
-                    pair_out, pairs, width, experts, top);
-    else if (dtype == 1)
-      launch_kernel(experts_identity_kernel<__nv_bfloat16>, dim3(iblocks), dim3(128), 0, stream, (const __nv_bfloat16*)x, ldx,
-                    chosen, weight, pair_out, pairs, width, experts, top);
-  }
   const int combine_top = fresh ? -top : top;
   if (tensor_cores && dtype == 1 && width % 8 == 0 && ff % 8 == 0 && ldx % 8 == 0) {
     const long long tiles = (pairs + TM - 1) / TM + (experts < pairs ? experts : pairs);
@@ -599,8 +583,9 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
         scale_input);
     const long long total = (long long)n_tokens * width;
     const long long blocks = (total + 255) / 256;
-    launch_kernel(experts_combine_kernel, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream, hidden, pair_out,
-                                                                                                total, width, combine_top);
+    launch_kernel(experts_combine_kernel<__nv_bfloat16>, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream,
+                  hidden, pair_out, total, width, combine_top, identity > 0 ? (const __nv_bfloat16*)x : nullptr, ldx, chosen,
+                  weight, experts);
     return launch_result();
   }
   // every expert may end with a partly filled tile
@@ -626,7 +611,12 @@ extern "C" int leone_experts_forward(int dtype, const void* x, int ldx, const vo
   }
   const long long total = (long long)n_tokens * width;
   const long long blocks = (total + 255) / 256;
-  launch_kernel(experts_combine_kernel, dim3((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8)), dim3(256), 0, stream, hidden, pair_out, total,
-                                                                                              width, combine_top);
+  const dim3 cgrid((unsigned)(blocks < 148 * 8 ? blocks : 148 * 8));
+  if (dtype == 0)
+    launch_kernel(experts_combine_kernel<float>, cgrid, dim3(256), 0, stream, hidden, pair_out, total, width, combine_top,
+                  identity > 0 ? (const float*)x : nullptr, ldx, chosen, weight, experts);
+  else
+    launch_kernel(experts_combine_kernel<__nv_bfloat16>, cgrid, dim3(256), 0, stream, hidden, pair_out, total, width,
+                  combine_top, identity > 0 ? (const __nv_bfloat16*)x : nullptr, ldx, chosen, weight, experts);
   return launch_result();
 }

@@ -143,15 +143,17 @@ gemm_batched_mma_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16
 // dst[t, :] (+)= coef * (a[t, :] / rms(a[t, :]) * w_a  [+ b[t, :] / rms(b[t, :]) * w_b]), every norm over its own
 // row with eps inside the root.  The norm of a sublayer's *output*, added to the residual stream (or
 // written, if not `accumulate`); with two sources, the normed outputs of two branches side by side.
-// `rounded`: also the new dst row in the run dtype, for the next reader of the stream.
+// `rounded`: also the new dst row in the run dtype, for the next reader of the stream.  `w_then`: the
+// combination is itself RMS-normed with that weight before it is added (a norm on the sum of normed branches).
 template <typename TW, typename TR>
 __global__ void __launch_bounds__(256)
 rms_norm_add_kernel(float* __restrict__ dst, const float* __restrict__ a, const TW* __restrict__ w_a,
                     const float* __restrict__ b, const TW* __restrict__ w_b, int width, float coef, float eps,
-                    int accumulate, TR* __restrict__ rounded) {
+                    int accumulate, TR* __restrict__ rounded, const TW* __restrict__ w_then) {
   pdl_trigger();
   pdl_wait();
   __shared__ float scratch[33];
+  extern __shared__ float row_s[];      // [width], only with w_then
   const size_t base = (size_t)blockIdx.x * width;
   float sa = 0.f, sb = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
@@ -165,10 +167,29 @@ rms_norm_add_kernel(float* __restrict__ dst, const float* __restrict__ a, const 
     sb = block_sum(sb, scratch);
     rb = 1.f / sqrtf(sb / (float)width + eps);
   }
+  float rt = 1.f;
+  if (w_then != nullptr) {
+    // the combined row is itself normed (with w_then) before it is added: a second pass over the row in shared memory
+    float st = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+      float v = a[base + c] * ra * to_float<TW>(w_a[c]);
+      if (b != nullptr) v += b[base + c] * rb * to_float<TW>(w_b[c]);
+      v *= coef;
+      row_s[c] = v;
+      st = fmaf(v, v, st);
+    }
+    st = block_sum(st, scratch);
+    rt = 1.f / sqrtf(st / (float)width + eps);
+  }
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float v = a[base + c] * ra * to_float<TW>(w_a[c]);
-    if (b != nullptr) v += b[base + c] * rb * to_float<TW>(w_b[c]);
-    v *= coef;
+    float v;
+    if (w_then != nullptr) {
+      v = row_s[c] * rt * to_float<TW>(w_then[c]);
+    } else {
+      v = a[base + c] * ra * to_float<TW>(w_a[c]);
+      if (b != nullptr) v += b[base + c] * rb * to_float<TW>(w_b[c]);
+      v *= coef;
+    }
     if (accumulate) v += dst[base + c];
     dst[base + c] = v;
     if (rounded != nullptr) rounded[base + c] = from_float<TR>(v);
@@ -276,15 +297,16 @@ extern "C" int leone_gemm_batched(int dtype, const void* a, const void* w, void*
 }
 
 // dst: fp32 [n, width]; a, b: fp32 [n, width] (b and w_b may be null); w in `w_dtype`; rounded: [n, width] in
-// `rounded_dtype`, or null.
+// `rounded_dtype`, or null; w_then: [width] in `w_dtype`, or null (width at most 12,000 with it).
 extern "C" int leone_rms_norm_add(float* dst, const float* a, const void* w_a, const float* b, const void* w_b,
                                   int w_dtype, int n, int width, float coef, float eps, int accumulate, void* rounded,
-                                  int rounded_dtype, cudaStream_t stream) {
+                                  int rounded_dtype, const void* w_then, cudaStream_t stream) {
   if (n <= 0) return 0;
-  if (width <= 0 || (b != nullptr) != (w_b != nullptr)) return kRefusedSize;
+  if (width <= 0 || (b != nullptr) != (w_b != nullptr) || (w_then != nullptr && width > 12000)) return kRefusedSize;
+  const size_t smem = w_then != nullptr ? sizeof(float) * (size_t)width : 0;
 #define NA(TW, TR)                                                                                                    \
-  return launch_kernel(rms_norm_add_kernel<TW, TR>, dim3(n), dim3(256), 0, stream, dst, a, (const TW*)w_a, b,         \
-                       (const TW*)w_b, width, coef, eps, accumulate, (TR*)rounded)
+  return launch_kernel(rms_norm_add_kernel<TW, TR>, dim3(n), dim3(256), smem, stream, dst, a, (const TW*)w_a, b,      \
+                       (const TW*)w_b, width, coef, eps, accumulate, (TR*)rounded, (const TW*)w_then)
   if (w_dtype == 0 && rounded_dtype == 0) NA(float, float);
   if (w_dtype == 0 && rounded_dtype == 1) NA(float, __nv_bfloat16);
   if (w_dtype == 1 && rounded_dtype == 0) NA(__nv_bfloat16, float);

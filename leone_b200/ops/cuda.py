@@ -848,9 +848,10 @@ class CudaOps:
         self.launches += 1
         _check(self.mixers.leone_zero(_ptr(t), ctypes.c_longlong(t.numel() * t.element_size()), self._stream()), "zero")
 
-    def rms_norm_add(self, dst, a, w_a, eps, b=None, w_b=None, coef=1.0, accumulate=True, rounded=None):
+    def rms_norm_add(self, dst, a, w_a, eps, b=None, w_b=None, coef=1.0, accumulate=True, rounded=None, then=None):
         """``dst (+)= coef * (rms_norm(a) * w_a [+ rms_norm(b) * w_b])``: fp32 rows, each source normed over
-        its own row; ``rounded``: also the new ``dst`` in another dtype (the stream for its next reader)."""
+        its own row; ``rounded``: also the new ``dst`` in another dtype (the stream for its next reader).
+        ``then``: a weight; the combination is itself RMS-normed with it (same eps) before it is added."""
         n, width = dst.shape
         _need(dst.dtype == torch.float32 and dst.is_contiguous() and a.dtype == torch.float32 and a.is_contiguous()
               and a.shape == dst.shape and w_a.numel() == width and w_a.is_contiguous(), "rms_norm_add layout")
@@ -859,11 +860,14 @@ class CudaOps:
                   and w_b.numel() == width and w_b.dtype == w_a.dtype and w_b.is_contiguous(), "rms_norm_add second source")
         if rounded is not None:
             _need(rounded.shape == dst.shape and rounded.is_contiguous(), "rms_norm_add rounded copy")
+        if then is not None:
+            _need(then.numel() == width and then.dtype == w_a.dtype and then.is_contiguous() and width <= 12000,
+                  "rms_norm_add: the norm after the combination")
         self.launches += 1
         _check(self.mixers.leone_rms_norm_add(
             _ptr(dst), _ptr(a), _ptr(w_a), _ptr(b), _ptr(w_b if b is not None else None), _dt(w_a.dtype), n, width,
             c_float(coef), c_float(eps), 1 if accumulate else 0, _ptr(rounded),
-            0 if rounded is None else _dt(rounded.dtype), self._stream()), "rms_norm_add")
+            0 if rounded is None else _dt(rounded.dtype), _ptr(then), self._stream()), "rms_norm_add")
 
     def gate_rows(self, a, gate, act="sigmoid"):
         """In place: ``a[t, c] *= act(gate[t, c])`` (``"sigmoid"`` or ``"silu"``); both in one dtype."""

@@ -170,8 +170,13 @@ class PostNormBlock(Block):
         rt = self.mixer.rt
         branch = rt.buffer("sublayer_out", hidden.shape[0], hidden.shape[1], torch.float32)
         x, copy = self._read(ctx, rt, hidden)
-        self._run(self.mixer, rt, branch, ctx, cache, x)
-        self.mixer_norm.add_normed(ctx, branch, hidden, rounded=copy)
+        folds = getattr(self.mixer, "adds_normed", None)
+        if folds is not None and folds(self.mixer_norm):
+            # the mixer adds its normed result itself (the norm folded into its last kernel)
+            self.mixer.forward(ctx, cache, x, hidden, normed_by=self.mixer_norm, rounded=copy)
+        else:
+            self._run(self.mixer, rt, branch, ctx, cache, x)
+            self.mixer_norm.add_normed(ctx, branch, hidden, rounded=copy)
         if self.feed_forward is not None:
             x, copy = self._read(ctx, rt, hidden)
             self._run(self.feed_forward, rt, branch, ctx, x)

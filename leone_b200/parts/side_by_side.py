@@ -23,6 +23,13 @@ from .base import CacheBundle, Mixer, WeightSpec
 class SideBySide(Mixer):
     writes_fresh = True           # forward(..., fresh=True) stores its result instead of adding it
 
+    def adds_normed(self, norm) -> bool:
+        """True if ``forward(..., normed_by=norm)`` can fold the arrangement's norm on this mixer's output into
+        its own combining kernel."""
+        return (self.combine == "normed_mean" and len(self.branches) == 2 and getattr(norm, "eps", None) == self.eps
+                and getattr(norm, "weight", None) is not None and norm.weight.dtype == self.norm_weights[0].dtype
+                and self.hidden <= 12000)
+
     def __init__(self, params, rt, position_encodings=None):
         super().__init__(params, rt)
         self.combine = params.get("combine", "sum")
@@ -70,7 +77,11 @@ class SideBySide(Mixer):
     def cache_request(self):
         return CacheBundle({name: part.cache_request() for name, part in self.branches})
 
-    def forward(self, ctx, cache, x, hidden, fresh=False):
+    def forward(self, ctx, cache, x, hidden, fresh=False, normed_by=None, rounded=None):
+        """``normed_by``: a norm part whose ``weight`` and ``eps`` norm this mixer's whole result before it is
+        added to ``hidden`` (the arrangement's norm on the mixer's output, folded into the combining kernel:
+        only offered to a mixer that declares ``adds_normed``, and only taken with two branches of the normed
+        mean and the same eps); ``rounded``: also the new ``hidden`` in the run dtype."""
         if self.combine == "sum":
             if fresh:
                 self.rt.ops.zero(hidden)
@@ -88,6 +99,11 @@ class SideBySide(Mixer):
                 part.forward(ctx, cache[name], x, out)
             outs.append(out)
         coef, w = 1.0 / len(outs), self.norm_weights
+        if normed_by is not None:
+            # hidden += norm(mean of the normed branches): the two norms after one another in one kernel
+            ops.rms_norm_add(hidden, outs[0], w[0], self.eps, b=outs[1], w_b=w[1], coef=coef, accumulate=True,
+                             rounded=rounded, then=normed_by.weight)
+            return
         # the normed outputs two at a time: one pass over the rows for a pair of branches
         for i in range(0, len(outs), 2):
             pair = i + 1 < len(outs)

@@ -416,13 +416,15 @@ class EmulatedOps:
     def zero(self, t):
         t.zero_()
 
-    def rms_norm_add(self, dst, a, w_a, eps, b=None, w_b=None, coef=1.0, accumulate=True, rounded=None):
+    def rms_norm_add(self, dst, a, w_a, eps, b=None, w_b=None, coef=1.0, accumulate=True, rounded=None, then=None):
         def normed(x, w):
             return x * torch.rsqrt((x * x).mean(dim=-1, keepdim=True) + eps) * w.float()
         v = normed(a, w_a)
         if b is not None:
             v = v + normed(b, w_b)
         v = coef * v
+        if then is not None:
+            v = normed(v, then)
         dst.copy_(dst + v if accumulate else v)
         if rounded is not None:
             rounded.copy_(dst.to(rounded.dtype))

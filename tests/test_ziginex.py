@@ -677,6 +677,11 @@ def test_small_kernels_against_their_definitions():
             want = (0.5 * (normed(a, wa) + normed(b, wb)) if two else normed(a, wa)) + (dst.double() if acc else 0)
             assert float((d.cpu().double() - want).abs().max()) < 1e-5
             assert torch.equal(rounded.cpu(), d.cpu().to(dtype))
+        # the mean of two normed rows, normed once more before it is added
+        d = dst.clone().cuda()
+        ops.rms_norm_add(d, a.cuda(), wa.cuda(), 1e-5, b=b.cuda(), w_b=wb.cuda(), coef=0.5, then=wb.cuda())
+        want = normed(0.5 * (normed(a, wa) + normed(b, wb)), wb) + dst.double()
+        assert float((d.cpu().double() - want).abs().max()) < 1e-5
         x, gate = torch.randn(n, width, generator=g).to(dtype), torch.randn(n, width + 3, generator=g).to(dtype)
         for act in ("sigmoid", "silu"):
             y = x.clone().cuda()
